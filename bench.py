@@ -1,0 +1,388 @@
+#!/usr/bin/env python
+"""Benchmark of the KV-page gather/scatter path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One step = gather every request of the batch out of the page pool into per-request
+worker tensors [layer, kv, token, head, dim], then scatter them back (a round trip).
+N = 1 runs the single-GPU configuration (Qwen2-7B-like geometry, 65,536-page pool, 64
+requests); N > 1 (under torchrun, one rank per GPU) stripes the pool by page id over
+the ranks and every rank gathers/scatters its own 64 requests, most pages remote.
+
+Prints ONE JSON line on rank 0.  `value` counts payload bytes (valid tokens) moved per
+second, both directions, inputs resident in HBM; `roofline.achieved` counts the bytes
+the kernel reads plus the bytes it writes (2 x payload per launch); `e2e` is the same
+round trip through the Python API from a host-resident plan, with the plan upload and
+a status read-back inside the timed region.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "kv_page_gather_scatter_throughput"
+UNIT = "GB/s"
+# DRAM bytes per payload byte of one launch, from the ncu capture summarised under
+# profiles/ (None until a capture exists).
+NCU_TRAFFIC_PER_PAYLOAD_BYTE = None
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--variant", default="auto", choices=["auto", "ldst", "bulk"])
+    ap.add_argument("--pool-pages", type=int, default=65536, help="pages per GPU")
+    ap.add_argument("--requests", type=int, default=64)
+    ap.add_argument("--small", action="store_true", help="profiling-sized case (2,048-page pool, 8 requests)")
+    ap.add_argument("--tune", action="append", default=[], metavar="KNOB=VALUE")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    return ap.parse_args()
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:  # noqa: BLE001
+        return 6650.0, "fallback"
+
+
+# --------------------------------------------------------------------------- clocks
+CLOCK_FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+                "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+                "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+
+class ClockSampler:
+    def __init__(self, device_index):
+        import torch
+        self.proc, self.path = None, None
+        try:
+            uuid = str(torch.cuda.get_device_properties(device_index).uuid)
+            ident = uuid if uuid.startswith("GPU-") else "GPU-" + uuid
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.out = open(self.path, "w")
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", ident, f"--query-gpu=timestamp,{CLOCK_FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "50"], stdout=self.out, stderr=subprocess.DEVNULL)
+        except Exception:  # noqa: BLE001
+            self.proc = None
+        self.t0 = self.t1 = None
+
+    def mark_start(self):
+        self.t0 = time.time()
+
+    def mark_end(self):
+        self.t1 = time.time()
+
+    def finish(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.12)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:  # noqa: BLE001
+            self.proc.kill()
+        self.out.close()
+        import datetime
+        rows = []
+        for line in open(self.path):
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                ts = datetime.datetime.strptime(parts[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                rows.append((ts, float(parts[1]), float(parts[2]), parts[4:9]))
+            except ValueError:
+                continue
+        os.unlink(self.path)
+        inside = [r for r in rows if self.t0 is not None and self.t0 - 0.05 <= r[0] <= self.t1 + 0.05]
+        use = inside if len(inside) >= 2 else rows
+        if not use:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({n for r in use for n, v in zip(names, r[3][1:]) if v.lower().startswith("active")})
+        return {"sm_mhz": statistics.median(r[1] for r in use), "sm_max_mhz": max(r[2] for r in use),
+                "reasons": reasons, "samples": len(use), "samples_in_timed_region": len(inside)}
+
+
+# --------------------------------------------------------------------------- CPU arm
+def cpu_reference_run(steps, warmup, requests, budget_s=20.0):
+    """The reference's CPU data path (token rows in host tensors, torch advanced indexing
+    over token indices: DistributedStorage/kvcache.py:38-43, Worker/Worker.py:57-62,207) as
+    restated in oracle/, on a bounded sample of the single-GPU workload: same geometry and
+    request-length distribution, 4,096-page pool, the first `sample_requests` requests."""
+    import torch
+
+    from bikv_b200 import workloads as W
+    from oracle import bikv_oracle as O
+
+    g = W.GEO_B
+    pool_pages, sample_requests = 4096, min(8, requests)
+    w = W.config1(seed=0, n_pages=pool_pages, n_requests=sample_requests)
+    plan = w.plan()
+    recs = plan.table.tolist()
+    src, dst = O.token_indices(recs, g.page_tokens)
+    gen = torch.Generator().manual_seed(0)
+    # N(0,1) values; one token row drawn per page slot and repeated (a copy's speed does
+    # not depend on the values, and drawing 1.9 G normals would dominate the run).
+    rows = torch.randn((g.page_tokens,) + g.token_shape, generator=gen, dtype=torch.float32).to(g.dtype)
+    pool = rows.repeat((pool_pages,) + (1,) * len(g.token_shape))
+    buf = torch.zeros((w.total_tokens,) + g.token_shape, dtype=g.dtype)
+    payload = w.payload_bytes
+
+    def step():
+        O.cpu_gather_tokens(pool, buf, src, dst)
+        O.cpu_scatter_tokens(pool, buf, src, dst)
+
+    for _ in range(max(1, min(warmup, 2))):
+        step()
+    times, t_all = [], time.perf_counter()
+    for _ in range(steps):
+        t = time.perf_counter()
+        step()
+        times.append(time.perf_counter() - t)
+        if time.perf_counter() - t_all > budget_s:
+            break
+    total = sum(times)
+    done = len(times)
+    gbs = 2 * payload * done / total / 1e9
+    sample = (f"{sample_requests} requests ({w.n_pages} pages, {payload / 1e9:.2f} GB payload) of the config-1 "
+              f"distribution on a {pool_pages}-page host pool, {done} round trips")
+    return {"value": gbs, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port", "sample": sample,
+            "ms_per_step": total / done * 1e3, "steps_done": done, "pages_per_s": 2 * w.n_pages * done / total,
+            "host_cpus": os.cpu_count()}
+
+
+def run_reference_arm(args, rank):
+    if rank != 0:
+        return
+    base = cpu_reference_run(args.steps, args.warmup, args.requests, budget_s=120.0)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": args.gpus,
+        "steps": base["steps_done"], "warmup": args.warmup, "ms_per_step": base["ms_per_step"],
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u16", "data": "synthetic",
+        "config": config_dict(args, None),
+        "cpu_baseline": {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")},
+        "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0, "pages_per_s": base["pages_per_s"], "host_cpus": base["host_cpus"],
+    }
+    print(json.dumps(line), flush=True)
+
+
+def config_dict(args, w):
+    name = "config1: Qwen2-7B-like KV (28 layers, 4 KV heads, head 128, bf16, 16-token pages)" if args.gpus == 1 \
+        else f"config2: config-1 geometry, pool striped page_id mod {args.gpus}, {args.gpus - 1}/{args.gpus} of pages remote"
+    c = {"workload": name, "pool_pages_per_gpu": args.pool_pages, "requests_per_gpu": args.requests,
+         "request_lengths": "lognormal(median 2048, sigma 0.8) clipped to [64, 8192]",
+         "step": "gather all requests + scatter them back",
+         "l2": "inputs larger than L2 (payload per launch is ~10 GB against 126 MB of L2)"}
+    if args.small:
+        c["workload"] += " [SMALL profiling case]"
+    if w is not None:
+        c.update({"pages_per_step_per_gpu": 2 * w.n_pages, "payload_bytes_per_direction_per_gpu": w.payload_bytes,
+                  "page_bytes": w.geom.page_bytes})
+    return c
+
+
+# --------------------------------------------------------------------------- GPU arm
+def main():
+    args = parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.small:
+        args.pool_pages, args.requests = 2048, 8
+    if args.impl == "reference":
+        run_reference_arm(args, rank)
+        return
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("--gpus N > 1 must be launched with torchrun (one rank per GPU)")
+        raise SystemExit(f"WORLD_SIZE={world} but --gpus {args.gpus}")
+
+    import torch
+    import torch.distributed as dist
+
+    import bikv_b200 as B
+    from bikv_b200 import _native as N
+    from bikv_b200 import workloads as W
+    from bikv_b200.plan import build_plan
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the KV-page path has no CPU implementation")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device(f"cuda:{local_rank}")
+    lib = N.lib()
+    for kv in args.tune:
+        k, v = kv.split("=")
+        N.check(lib.bikv_set_tuning(k.encode(), int(v)), f"tune {k}")
+    variant = {"auto": N.VARIANT_AUTO, "ldst": N.VARIANT_LDST, "bulk": N.VARIANT_BULK}[args.variant]
+
+    multi = world > 1
+    if multi:
+        dist.init_process_group("nccl", device_id=dev)
+        cpu_group = dist.new_group(backend="gloo")
+
+    geom = W.GEO_B
+    shard = B.ShardedPool.allocate_shard(geom, args.pool_pages, dev)
+    W.fill_normal_(shard, seed=1234 + rank)
+    if multi:
+        pool = B.ShardedPool.exchange(shard, geom, group=cpu_group)
+        w = W.config2(rank, world, seed=0, pages_per_shard=args.pool_pages, n_requests=args.requests)
+    else:
+        pool = B.ShardedPool.single(shard, geom)
+        w = W.config1(seed=0, n_pages=args.pool_pages, n_requests=args.requests)
+    plan = w.plan()
+    tensors = [torch.zeros(geom.worker_shape(int(t)), dtype=geom.dtype, device=dev) for t in w.request_tokens]
+    mover = B.PageMover(dev, variant=variant)
+    d_recs, d_reqs = mover.upload(plan, geom, tensors)
+    stream = torch.cuda.current_stream(dev)
+
+    def barrier():
+        if multi:
+            dist.barrier(group=cpu_group)
+
+    def step_resident():
+        mover.gather_dev(pool, d_recs, d_reqs)
+        mover.scatter_dev(pool, d_recs, d_reqs)
+
+    flat_begin = w.flat()
+    item_tokens = w.request_tokens.astype("int32")
+    item_req = __import__("numpy").arange(w.n_requests, dtype="int32")
+
+    def step_e2e():
+        p = build_plan(flat_begin, item_tokens, geom.page_tokens, item_request=item_req, n_requests=w.n_requests)
+        mover.gather(pool, p, tensors)
+        mover.scatter(pool, p, tensors)
+        mover.check_status()          # 16-byte device->host read, synchronises the step
+
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    for _ in range(args.warmup):
+        step_resident()
+    torch.cuda.synchronize()
+
+    # ---- timed region: K resident steps, CUDA events on the launching stream ----
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
+    launches0 = lib.bikv_launch_count()
+    barrier()
+    torch.cuda.synchronize()
+    if sampler:
+        sampler.mark_start()
+    t_begin = torch.cuda.Event(enable_timing=True)
+    t_end = torch.cuda.Event(enable_timing=True)
+    t_begin.record(stream)
+    for k in range(args.steps):
+        ev[k][0].record(stream)
+        mover.gather_dev(pool, d_recs, d_reqs)
+        ev[k][1].record(stream)
+        mover.scatter_dev(pool, d_recs, d_reqs)
+        ev[k][2].record(stream)
+    t_end.record(stream)
+    torch.cuda.synchronize()
+    barrier()
+    if sampler:
+        sampler.mark_end()
+    launches = lib.bikv_launch_count() - launches0
+    elapsed_ms = t_begin.elapsed_time(t_end)
+    gather_ms = [e[0].elapsed_time(e[1]) for e in ev]
+    scatter_ms = [e[1].elapsed_time(e[2]) for e in ev]
+    mover.check_status()
+
+    # ---- end to end through the Python API, host-resident plan ----
+    e2e = None
+    if not args.no_e2e:
+        for _ in range(max(1, min(args.warmup, 3))):
+            step_e2e()
+        barrier()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            step_e2e()
+        torch.cuda.synchronize()
+        e2e_s = time.perf_counter() - t0
+        barrier()
+        h2d = 2 * (plan.n_pages * 16 + w.n_requests * 16)
+        e2e = {"seconds": e2e_s, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 16}
+
+    clocks = sampler.finish() if sampler else None
+
+    # ---- max over ranks ----
+    payload = w.payload_bytes
+    pages = w.n_pages
+    if multi:
+        t = torch.tensor([elapsed_ms, e2e["seconds"] if e2e else 0.0], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        tot = torch.tensor([float(payload), float(pages), float(launches)], dtype=torch.float64, device=dev)
+        dist.all_reduce(tot, op=dist.ReduceOp.SUM)
+        elapsed_ms = float(t[0])
+        if e2e:
+            e2e["seconds"] = float(t[1])
+        total_payload, total_pages, total_launches = float(tot[0]), float(tot[1]), int(tot[2])
+    else:
+        total_payload, total_pages, total_launches = float(payload), float(pages), launches
+
+    if rank == 0:
+        peak, peak_kind = measured_peaks()
+        secs = elapsed_ms / 1e3
+        value = 2 * total_payload * args.steps / secs / 1e9
+        launch_ms = statistics.mean(gather_ms + scatter_ms)
+        achieved = 2 * payload / (launch_ms / 1e3) / 1e9
+        kernel = {N.VARIANT_LDST: "k_paged_ldst", N.VARIANT_BULK: "k_paged_bulk"}[
+            variant if variant != N.VARIANT_AUTO else int(lib.bikv_get_tuning(b"auto_variant"))]
+        roofline = {
+            "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+            "traffic": None if NCU_TRAFFIC_PER_PAYLOAD_BYTE is None else NCU_TRAFFIC_PER_PAYLOAD_BYTE * payload,
+            "peak_kind": f"of {peak_kind}", "kernel": kernel,
+            "algorithmic_bytes_per_launch": 2 * payload, "launch_ms": launch_ms,
+            "gather_ms": statistics.mean(gather_ms), "scatter_ms": statistics.mean(scatter_ms),
+            "note": "rank 0's launches; local pages are HBM-bound, remote pages NVLink-bound" if multi else
+                    "each payload byte is read once and written once",
+        }
+        if multi:
+            remote = w.remote_fraction(rank)
+            nv = remote * payload / (statistics.mean(gather_ms) / 1e3) / 1e9
+            roofline["nvlink"] = {"remote_fraction": remote, "gather_ingress_GBps_per_gpu": nv,
+                                  "frac_of_770_measured": nv / 770.0, "frac_of_900_nominal": nv / 900.0,
+                                  "scatter_egress_GBps_per_gpu": remote * payload / (statistics.mean(scatter_ms) / 1e3) / 1e9}
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "u16", "data": "synthetic",
+            "config": config_dict(args, w), "pages_per_s": 2 * total_pages * args.steps / secs,
+            "roofline": roofline, "gpu_launches": total_launches, "clocks": clocks,
+        }
+        if e2e:
+            line["e2e"] = {"value": 2 * total_payload * args.steps / e2e["seconds"] / 1e9, "unit": UNIT,
+                           "h2d_bytes_per_step": e2e["h2d_bytes_per_step"],
+                           "d2h_bytes_per_step": e2e["d2h_bytes_per_step"],
+                           "ms_per_step": e2e["seconds"] / args.steps * 1e3,
+                           "what": "build_plan from page lists + PageMover.gather + PageMover.scatter + status read, "
+                                   "plan in pinned host memory; the pool and the worker KV tensors stay in HBM"}
+        if not multi and not args.no_cpu_baseline:
+            base = cpu_reference_run(20, 1, args.requests, budget_s=15.0)
+            line["cpu_baseline"] = {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")}
+        print(json.dumps(line), flush=True)
+
+    if multi:
+        barrier()
+        pool.close()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,553 @@
+// Host side of libbikv.so: argument checking, plan building/validation,
+// launch configuration and the peer / IPC plumbing.  See include/bikv.h for the
+// contract of every entry point.
+#include "bikv_kernels.cuh"
+
+#include <algorithm>
+#include <atomic>
+#include <cstring>
+#include <mutex>
+#include <vector>
+
+namespace {
+
+using namespace bikv;
+
+thread_local int tl_cuda_error = 0;
+std::atomic<long long> g_launches{0};
+
+// Tuning knobs (plain atomics: readers take a snapshot per call).
+std::atomic<long long> g_ldst_ctas_per_sm{8};
+std::atomic<long long> g_bulk_ctas_per_sm{3};
+std::atomic<long long> g_bulk_stages{4};
+std::atomic<long long> g_seg_bytes{16384};
+std::atomic<long long> g_auto_variant{BIKV_VARIANT_LDST};
+
+int cuda_fail(cudaError_t e) {
+  tl_cuda_error = (int)e;
+  return BIKV_ERR_CUDA;
+}
+#define BIKV_CUDA(expr)                                \
+  do {                                                 \
+    cudaError_t e__ = (expr);                          \
+    if (e__ != cudaSuccess) return cuda_fail(e__);     \
+  } while (0)
+
+struct DeviceInfo {
+  int sm_count = 0;
+  int max_optin_smem = 0;
+};
+std::mutex g_dev_mu;
+DeviceInfo g_dev[64];
+bool g_dev_known[64] = {false};
+
+int device_info(DeviceInfo* out) {
+  int dev = 0;
+  BIKV_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return BIKV_ERR_BAD_ARG;
+  std::lock_guard<std::mutex> lk(g_dev_mu);
+  if (!g_dev_known[dev]) {
+    BIKV_CUDA(cudaDeviceGetAttribute(&g_dev[dev].sm_count, cudaDevAttrMultiProcessorCount, dev));
+    BIKV_CUDA(cudaDeviceGetAttribute(&g_dev[dev].max_optin_smem,
+                                     cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+    g_dev_known[dev] = true;
+  }
+  *out = g_dev[dev];
+  return BIKV_OK;
+}
+
+int check_geometry(const bikv_geometry* g) {
+  if (!g) return BIKV_ERR_BAD_ARG;
+  if (g->n_layers <= 0 || g->n_kv_heads <= 0 || g->head_dim <= 0 || g->page_tokens <= 0)
+    return BIKV_ERR_BAD_ARG;
+  if (g->elt_bytes != 1 && g->elt_bytes != 2 && g->elt_bytes != 4) return BIKV_ERR_BAD_ARG;
+  if (g->pool_layout != BIKV_POOL_PAGED && g->pool_layout != BIKV_POOL_TOKEN_MAJOR)
+    return BIKV_ERR_BAD_ARG;
+  const long long row = (long long)g->n_kv_heads * g->head_dim * g->elt_bytes;
+  if (g->pool_layout == BIKV_POOL_PAGED) {
+    if (row % 16 != 0) return BIKV_ERR_ALIGNMENT;
+  } else {
+    // 16-byte worker vectors run along dim.
+    if (((long long)g->head_dim * g->elt_bytes) % 16 != 0) return BIKV_ERR_ALIGNMENT;
+  }
+  if (row * g->page_tokens > (1ll << 30)) return BIKV_ERR_TOO_LARGE;
+  return BIKV_OK;
+}
+
+int check_pool(const bikv_pool_desc* p) {
+  if (!p) return BIKV_ERR_BAD_ARG;
+  if (p->n_shards <= 0 || p->n_shards > BIKV_MAX_SHARDS) return BIKV_ERR_BAD_ARG;
+  if (p->pages_per_shard <= 0) return BIKV_ERR_BAD_ARG;
+  if (p->shard_rule != BIKV_SHARD_MOD && p->shard_rule != BIKV_SHARD_BLOCK) return BIKV_ERR_BAD_ARG;
+  if (p->pages_per_shard * p->n_shards > 0x7fffffffll) return BIKV_ERR_TOO_LARGE;
+  for (int s = 0; s < p->n_shards; ++s) {
+    if (!p->shard_base[s]) return BIKV_ERR_BAD_ARG;
+    if (((uintptr_t)p->shard_base[s]) & 15) return BIKV_ERR_ALIGNMENT;
+  }
+  return BIKV_OK;
+}
+
+PoolDev to_dev(const bikv_pool_desc* p) {
+  PoolDev d;
+  memset(&d, 0, sizeof(d));
+  for (int s = 0; s < p->n_shards; ++s) d.base[s] = (char*)p->shard_base[s];
+  d.n_shards = p->n_shards;
+  d.rule = p->shard_rule;
+  d.pages_per_shard = p->pages_per_shard;
+  return d;
+}
+
+int after_launch() {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return cuda_fail(e);
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return BIKV_OK;
+}
+
+int launch_token_major(const bikv_pool_desc* pool, const bikv_geometry* g, const bikv_page_rec* recs,
+                       long long n_pages, const bikv_request_desc* reqs, int to_pool,
+                       cudaStream_t st) {
+  DeviceInfo di;
+  int rc = device_info(&di);
+  if (rc) return rc;
+  const unsigned V = 16 / g->elt_bytes;
+  const unsigned C = 2u * g->n_layers;
+  const unsigned H = g->n_kv_heads, D = g->head_dim;
+  // Largest slab (DT d-values) that divides D, is a multiple of V and stays
+  // within 48 KiB of shared memory so several CTAs share an SM.
+  const long long per_d = (long long)H * C * g->elt_bytes;
+  unsigned DT = 0;
+  for (unsigned cand = D; cand >= V; --cand) {
+    if (D % cand || cand % V) continue;
+    if (per_d * cand <= 48 * 1024) {
+      DT = cand;
+      break;
+    }
+  }
+  if (DT == 0) {
+    // Even one vector of d exceeds 48 KiB: take the opt-in limit.
+    DT = V;
+    if (per_d * DT > di.max_optin_smem) return BIKV_ERR_TOO_LARGE;
+  }
+  const long long smem = per_d * DT;
+  const long long items = n_pages * g->page_tokens * (long long)(D / DT);
+  if (items > 0x7fffffffll) return BIKV_ERR_TOO_LARGE;
+  TokenMajorArgs a;
+  memset(&a, 0, sizeof(a));
+  a.recs = reinterpret_cast<const uint4*>(recs);
+  a.reqs = reqs;
+  a.pool = to_dev(pool);
+  a.n_items = (unsigned)items;
+  a.page_tokens = g->page_tokens;
+  a.slabs = D / DT;
+  a.DT = DT;
+  a.H = H;
+  a.D = D;
+  a.C = C;
+  a.token_bytes = (unsigned long long)per_d * D;
+  a.to_pool = to_pool;
+  const int threads = 256;
+  int per_sm = (int)std::max<long long>(1, std::min<long long>(8, (200 * 1024) / std::max<long long>(smem, 1)));
+  unsigned grid = (unsigned)std::min<long long>(items, (long long)di.sm_count * per_sm);
+  if (grid == 0) return BIKV_OK;
+  auto launch = [&](auto kern) -> int {
+    if (smem > 48 * 1024)
+      BIKV_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    kern<<<grid, threads, (size_t)smem, st>>>(a);
+    return after_launch();
+  };
+  switch (g->elt_bytes) {
+    case 1: return launch(k_token_major<uint8_t>);
+    case 2: return launch(k_token_major<uint16_t>);
+    default: return launch(k_token_major<uint32_t>);
+  }
+}
+
+int launch_paged(const bikv_pool_desc* pool, const bikv_geometry* g, const bikv_page_rec* recs,
+                 long long n_pages, const bikv_request_desc* reqs, int to_pool, int variant,
+                 int32_t* status, cudaStream_t st) {
+  DeviceInfo di;
+  int rc = device_info(&di);
+  if (rc) return rc;
+  if (variant == BIKV_VARIANT_AUTO) variant = (int)g_auto_variant.load();
+  if (variant != BIKV_VARIANT_LDST && variant != BIKV_VARIANT_BULK) return BIKV_ERR_BAD_ARG;
+  if (variant == BIKV_VARIANT_BULK && !status) return BIKV_ERR_BAD_ARG;
+
+  PagedArgs a;
+  memset(&a, 0, sizeof(a));
+  a.recs = reinterpret_cast<const uint4*>(recs);
+  a.reqs = reqs;
+  a.pool = to_dev(pool);
+  a.planes = 2u * g->n_layers;
+  a.row_bytes = (unsigned)(g->n_kv_heads * g->head_dim * g->elt_bytes);
+  a.plane_bytes = a.row_bytes * g->page_tokens;
+  a.page_bytes = (unsigned long long)a.plane_bytes * a.planes;
+  unsigned seg = (unsigned)g_seg_bytes.load();
+  if (seg > a.plane_bytes) seg = a.plane_bytes;  // plane_bytes is a multiple of 16
+  a.seg_bytes = seg;
+  a.parts = (a.plane_bytes + seg - 1) / seg;
+  const long long items = n_pages * (long long)a.planes * a.parts;
+  if (items > 0x7fffffffll) return BIKV_ERR_TOO_LARGE;
+  a.n_items = (unsigned)items;
+  a.to_pool = to_pool;
+  a.status = status;
+  if (items == 0) return BIKV_OK;
+
+  if (variant == BIKV_VARIANT_LDST) {
+    const int threads = 256, warps = threads / 32;
+    const long long want = (items + warps - 1) / warps;
+    unsigned grid = (unsigned)std::min<long long>(want, (long long)di.sm_count * g_ldst_ctas_per_sm.load());
+    k_paged_ldst<8><<<grid, threads, 0, st>>>(a);
+    return after_launch();
+  }
+  int stages = (int)g_bulk_stages.load();
+  long long per_sm = g_bulk_ctas_per_sm.load();
+  const long long budget = std::min<long long>(di.max_optin_smem, 227 * 1024) - 1024;
+  while (stages > 2 && (long long)stages * seg > budget) --stages;
+  if ((long long)stages * seg > budget) return BIKV_ERR_TOO_LARGE;
+  const long long smem = (long long)stages * seg;
+  while (per_sm > 1 && per_sm * (smem + 1024) > 227 * 1024) --per_sm;
+  unsigned grid = (unsigned)std::min<long long>(items, (long long)di.sm_count * per_sm);
+  if (smem > 48 * 1024)
+    BIKV_CUDA(cudaFuncSetAttribute(k_paged_bulk, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  k_paged_bulk<<<grid, 32, (size_t)smem, st>>>(a, stages);
+  return after_launch();
+}
+
+int run(const bikv_pool_desc* pool, const bikv_geometry* geom, const bikv_page_rec* recs_dev,
+        int64_t n_pages, const bikv_request_desc* reqs_dev, int32_t n_requests, int to_pool,
+        int variant, int32_t* status_dev, void* stream) {
+  int rc = check_geometry(geom);
+  if (rc) return rc;
+  rc = check_pool(pool);
+  if (rc) return rc;
+  if (n_pages < 0 || n_requests < 0) return BIKV_ERR_BAD_ARG;
+  if (n_pages == 0) return BIKV_OK;
+  if (!recs_dev || !reqs_dev || n_requests == 0) return BIKV_ERR_BAD_ARG;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (geom->pool_layout == BIKV_POOL_TOKEN_MAJOR)
+    return launch_token_major(pool, geom, recs_dev, n_pages, reqs_dev, to_pool, st);
+  return launch_paged(pool, geom, recs_dev, n_pages, reqs_dev, to_pool, variant, status_dev, st);
+}
+
+int run_h(const bikv_pool_desc* pool, const bikv_geometry* geom, const bikv_page_rec* recs_host,
+          int64_t n_pages, const bikv_request_desc* reqs_host, int32_t n_requests, void* scratch,
+          int64_t scratch_bytes, int validate, int to_pool, int variant, int32_t* status_dev,
+          void* stream) {
+  if (n_pages < 0 || n_requests < 0) return BIKV_ERR_BAD_ARG;
+  if (n_pages == 0) return BIKV_OK;
+  if (!recs_host || !reqs_host || !scratch) return BIKV_ERR_BAD_ARG;
+  for (int32_t r = 0; r < n_requests; ++r)
+    if (!reqs_host[r].base) return BIKV_ERR_BAD_ARG;
+  if (validate) {
+    int rc = bikv_plan_validate(recs_host, n_pages, reqs_host, n_requests, pool, geom, to_pool);
+    if (rc) return rc;
+  }
+  const int64_t need = bikv_plan_scratch_bytes(n_pages, n_requests);
+  if (scratch_bytes < need) return BIKV_ERR_TOO_LARGE;
+  if (((uintptr_t)scratch) & 15) return BIKV_ERR_ALIGNMENT;
+  cudaStream_t st = (cudaStream_t)stream;
+  char* d_recs = (char*)scratch;
+  const size_t rec_bytes = (size_t)n_pages * sizeof(bikv_page_rec);
+  char* d_reqs = d_recs + ((rec_bytes + 255) & ~(size_t)255);
+  BIKV_CUDA(cudaMemcpyAsync(d_recs, recs_host, rec_bytes, cudaMemcpyHostToDevice, st));
+  BIKV_CUDA(cudaMemcpyAsync(d_reqs, reqs_host, (size_t)n_requests * sizeof(bikv_request_desc),
+                            cudaMemcpyHostToDevice, st));
+  return run(pool, geom, (const bikv_page_rec*)d_recs, n_pages, (const bikv_request_desc*)d_reqs,
+             n_requests, to_pool, variant, status_dev, stream);
+}
+
+struct Knob {
+  const char* name;
+  std::atomic<long long>* v;
+  long long lo, hi;
+};
+Knob* find_knob(const char* name) {
+  static Knob knobs[] = {
+      {"ldst_ctas_per_sm", &g_ldst_ctas_per_sm, 1, 32},
+      {"bulk_ctas_per_sm", &g_bulk_ctas_per_sm, 1, 16},
+      {"bulk_stages", &g_bulk_stages, 2, kMaxStages},
+      {"seg_bytes", &g_seg_bytes, 1024, 64 * 1024},
+      {"auto_variant", &g_auto_variant, BIKV_VARIANT_LDST, BIKV_VARIANT_BULK},
+  };
+  if (!name) return nullptr;
+  for (auto& k : knobs)
+    if (!strcmp(k.name, name)) return &k;
+  return nullptr;
+}
+
+}  // namespace
+
+extern "C" {
+
+int bikv_version(void) { return BIKV_ABI_VERSION; }
+
+const char* bikv_strerror(int status) {
+  switch (status) {
+    case BIKV_OK: return "ok";
+    case BIKV_ERR_BAD_ARG: return "bad argument";
+    case BIKV_ERR_PAGE_RANGE: return "page id outside the pool";
+    case BIKV_ERR_DST_RANGE: return "token window outside the request tensor";
+    case BIKV_ERR_ALIGNMENT: return "address or row not 16-byte aligned";
+    case BIKV_ERR_PEER: return "peer access or IPC mapping unavailable";
+    case BIKV_ERR_CUDA: return "CUDA call failed (see bikv_last_cuda_error)";
+    case BIKV_ERR_OVERLAP: return "scatter plan names a pool page twice";
+    case BIKV_ERR_DEVICE_TIMEOUT: return "bounded device wait ran out";
+    case BIKV_ERR_TOO_LARGE: return "size beyond a documented maximum";
+    case BIKV_ERR_PLAN: return "inconsistent plan";
+    default: return "unknown status";
+  }
+}
+
+int bikv_last_cuda_error(void) { return tl_cuda_error; }
+int64_t bikv_launch_count(void) { return g_launches.load(); }
+
+int bikv_set_tuning(const char* name, int64_t value) {
+  Knob* k = find_knob(name);
+  if (!k || value < k->lo || value > k->hi) return BIKV_ERR_BAD_ARG;
+  if (!strcmp(name, "seg_bytes") && (value % 1024) != 0) return BIKV_ERR_BAD_ARG;
+  k->v->store(value);
+  return BIKV_OK;
+}
+int64_t bikv_get_tuning(const char* name) {
+  Knob* k = find_knob(name);
+  return k ? k->v->load() : (int64_t)BIKV_ERR_BAD_ARG;
+}
+
+int64_t bikv_plan_build(const int32_t* pages_flat, const int64_t* item_page_begin,
+                        const int32_t* item_tokens, const int32_t* item_request,
+                        const int32_t* item_shard, int64_t pages_per_shard, int32_t n_items,
+                        int32_t page_tokens, int64_t* request_tokens, int32_t n_requests,
+                        bikv_page_rec* out, int64_t out_capacity) {
+  if (n_items < 0 || page_tokens <= 0 || n_requests <= 0) return BIKV_ERR_BAD_ARG;
+  if (n_items == 0) return 0;
+  if (!item_page_begin || !item_tokens || !request_tokens || !out) return BIKV_ERR_BAD_ARG;
+  if (item_shard && pages_per_shard <= 0) return BIKV_ERR_BAD_ARG;
+  int64_t n = 0;
+  for (int32_t it = 0; it < n_items; ++it) {
+    const int64_t b = item_page_begin[it], e = item_page_begin[it + 1];
+    if (b < 0 || e < b) return BIKV_ERR_PLAN;
+    const int32_t req = item_request ? item_request[it] : 0;
+    if (req < 0 || req >= n_requests) return BIKV_ERR_BAD_ARG;
+    const int32_t tokens = item_tokens[it];
+    if (tokens < 0) return BIKV_ERR_PLAN;
+    if (e > b && !pages_flat) return BIKV_ERR_BAD_ARG;
+    const int32_t rem = tokens % page_tokens;
+    for (int64_t p = b; p < e; ++p) {
+      // Tail rule of the reference: only the LAST page of an item is short,
+      // and only when the token count is not a multiple of the page size.
+      const int32_t size = (p == e - 1 && rem != 0) ? rem : page_tokens;
+      if (n >= out_capacity) return BIKV_ERR_TOO_LARGE;
+      const int64_t off = request_tokens[req];
+      if (off > 0x7fffffffll - size) return BIKV_ERR_TOO_LARGE;
+      int64_t id = pages_flat[p];
+      if (item_shard) {
+        if (id < 0 || id >= pages_per_shard) return BIKV_ERR_PAGE_RANGE;
+        id += (int64_t)item_shard[it] * pages_per_shard;
+        if (id > 0x7fffffffll) return BIKV_ERR_TOO_LARGE;
+      }
+      out[n].page_id = (int32_t)id;
+      out[n].valid_tokens = size;
+      out[n].request = req;
+      out[n].token_offset = (int32_t)off;
+      request_tokens[req] = off + size;
+      ++n;
+    }
+  }
+  return n;
+}
+
+int bikv_plan_validate(const bikv_page_rec* recs, int64_t n_pages, const bikv_request_desc* requests,
+                       int32_t n_requests, const bikv_pool_desc* pool, const bikv_geometry* geom,
+                       int check_overlap) {
+  int rc = check_geometry(geom);
+  if (rc) return rc;
+  rc = check_pool(pool);
+  if (rc) return rc;
+  if (n_pages < 0 || n_requests < 0) return BIKV_ERR_BAD_ARG;
+  if (n_pages == 0) return BIKV_OK;
+  if (!recs || !requests || n_requests == 0) return BIKV_ERR_BAD_ARG;
+  const int64_t total_pages = pool->pages_per_shard * pool->n_shards;
+  for (int32_t r = 0; r < n_requests; ++r) {
+    if (requests[r].tokens < 0) return BIKV_ERR_BAD_ARG;
+    if (requests[r].base && (((uintptr_t)requests[r].base) & 15)) return BIKV_ERR_ALIGNMENT;
+  }
+  for (int64_t i = 0; i < n_pages; ++i) {
+    const bikv_page_rec& p = recs[i];
+    if (p.page_id < 0 || p.page_id >= total_pages) return BIKV_ERR_PAGE_RANGE;
+    if (p.valid_tokens < 1 || p.valid_tokens > geom->page_tokens) return BIKV_ERR_PLAN;
+    if (p.request < 0 || p.request >= n_requests) return BIKV_ERR_BAD_ARG;
+    if (p.token_offset < 0 || (int64_t)p.token_offset + p.valid_tokens > requests[p.request].tokens)
+      return BIKV_ERR_DST_RANGE;
+  }
+  if (check_overlap) {
+    std::vector<int32_t> ids((size_t)n_pages);
+    for (int64_t i = 0; i < n_pages; ++i) ids[(size_t)i] = recs[i].page_id;
+    std::sort(ids.begin(), ids.end());
+    if (std::adjacent_find(ids.begin(), ids.end()) != ids.end()) return BIKV_ERR_OVERLAP;
+  }
+  return BIKV_OK;
+}
+
+int bikv_gather(const bikv_pool_desc* pool, const bikv_geometry* geom, const bikv_page_rec* recs_dev,
+                int64_t n_pages, const bikv_request_desc* requests_dev, int32_t n_requests,
+                int variant, int32_t* status_dev, void* stream) {
+  return run(pool, geom, recs_dev, n_pages, requests_dev, n_requests, 0, variant, status_dev, stream);
+}
+
+int bikv_scatter(const bikv_pool_desc* pool, const bikv_geometry* geom, const bikv_page_rec* recs_dev,
+                 int64_t n_pages, const bikv_request_desc* requests_dev, int32_t n_requests,
+                 int variant, int32_t* status_dev, void* stream) {
+  return run(pool, geom, recs_dev, n_pages, requests_dev, n_requests, 1, variant, status_dev, stream);
+}
+
+int64_t bikv_plan_scratch_bytes(int64_t n_pages, int32_t n_requests) {
+  if (n_pages < 0 || n_requests < 0) return BIKV_ERR_BAD_ARG;
+  const int64_t rec = ((int64_t)n_pages * (int64_t)sizeof(bikv_page_rec) + 255) & ~(int64_t)255;
+  const int64_t req = ((int64_t)n_requests * (int64_t)sizeof(bikv_request_desc) + 255) & ~(int64_t)255;
+  return rec + req;
+}
+
+int bikv_gather_h(const bikv_pool_desc* pool, const bikv_geometry* geom, const bikv_page_rec* recs_host,
+                  int64_t n_pages, const bikv_request_desc* requests_host, int32_t n_requests,
+                  void* plan_scratch_dev, int64_t plan_scratch_bytes, int validate, int variant,
+                  int32_t* status_dev, void* stream) {
+  return run_h(pool, geom, recs_host, n_pages, requests_host, n_requests, plan_scratch_dev,
+               plan_scratch_bytes, validate, 0, variant, status_dev, stream);
+}
+
+int bikv_scatter_h(const bikv_pool_desc* pool, const bikv_geometry* geom, const bikv_page_rec* recs_host,
+                   int64_t n_pages, const bikv_request_desc* requests_host, int32_t n_requests,
+                   void* plan_scratch_dev, int64_t plan_scratch_bytes, int validate, int variant,
+                   int32_t* status_dev, void* stream) {
+  return run_h(pool, geom, recs_host, n_pages, requests_host, n_requests, plan_scratch_dev,
+               plan_scratch_bytes, validate, 1, variant, status_dev, stream);
+}
+
+int bikv_copy_pages_flat(const void* src, void* dst, const int64_t* src_off_dev,
+                         const int64_t* dst_off_dev, int64_t n_pages, int64_t page_elems,
+                         int32_t elt_bytes, void* stream) {
+  if (n_pages < 0 || page_elems < 0 || elt_bytes <= 0 || elt_bytes > 16) return BIKV_ERR_BAD_ARG;
+  if (n_pages == 0 || page_elems == 0) return BIKV_OK;
+  if (!src || !dst) return BIKV_ERR_BAD_ARG;
+  DeviceInfo di;
+  int rc = device_info(&di);
+  if (rc) return rc;
+  FlatArgs a;
+  memset(&a, 0, sizeof(a));
+  a.src = (const char*)src;
+  a.dst = (char*)dst;
+  a.src_off = (const long long*)src_off_dev;
+  a.dst_off = (const long long*)dst_off_dev;
+  a.page_bytes = (unsigned long long)page_elems * elt_bytes;
+  a.seg_bytes = (unsigned)g_seg_bytes.load();
+  const unsigned long long parts = (a.page_bytes + a.seg_bytes - 1) / a.seg_bytes;
+  if (parts > 0x7fffffffull) return BIKV_ERR_TOO_LARGE;
+  a.parts = (unsigned)parts;
+  a.n_items = (unsigned long long)n_pages * parts;
+  a.elt_bytes = (unsigned)elt_bytes;
+  const int threads = 256, warps = threads / 32;
+  const unsigned long long want = (a.n_items + warps - 1) / warps;
+  unsigned grid = (unsigned)std::min<unsigned long long>(
+      want, (unsigned long long)di.sm_count * g_ldst_ctas_per_sm.load());
+  k_flat<8><<<grid, threads, 0, (cudaStream_t)stream>>>(a);
+  return after_launch();
+}
+
+int bikv_copy_range(void* dst, const void* src, int64_t bytes, void* stream) {
+  if (bytes < 0) return BIKV_ERR_BAD_ARG;
+  return bikv_copy_pages_flat(src, dst, nullptr, nullptr, 1, bytes, 1, stream);
+}
+
+int bikv_can_access_peer(int device, int peer, int* can) {
+  if (!can) return BIKV_ERR_BAD_ARG;
+  if (device == peer) {
+    *can = 1;
+    return BIKV_OK;
+  }
+  BIKV_CUDA(cudaDeviceCanAccessPeer(can, device, peer));
+  return BIKV_OK;
+}
+
+int bikv_enable_peer(int device, int peer) {
+  if (device == peer) return BIKV_OK;
+  int can = 0;
+  BIKV_CUDA(cudaDeviceCanAccessPeer(&can, device, peer));
+  if (!can) return BIKV_ERR_PEER;
+  int prev = 0;
+  BIKV_CUDA(cudaGetDevice(&prev));
+  BIKV_CUDA(cudaSetDevice(device));
+  cudaError_t e = cudaDeviceEnablePeerAccess(peer, 0);
+  if (e == cudaErrorPeerAccessAlreadyEnabled) {
+    (void)cudaGetLastError();
+    e = cudaSuccess;
+  }
+  cudaError_t e2 = cudaSetDevice(prev);
+  if (e != cudaSuccess) {
+    cuda_fail(e);
+    return BIKV_ERR_PEER;
+  }
+  BIKV_CUDA(e2);
+  return BIKV_OK;
+}
+
+int bikv_pool_export(void* ptr, unsigned char handle[64], int64_t* offset) {
+  if (!ptr || !handle || !offset) return BIKV_ERR_BAD_ARG;
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "CUDA IPC handle is 64 bytes");
+  // The handle names the whole allocation; find its base through the driver
+  // entry point (no link-time dependency on libcuda).
+  typedef int (*get_range_fn)(unsigned long long*, size_t*, unsigned long long);
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  BIKV_CUDA(cudaGetDriverEntryPoint("cuMemGetAddressRange", &fn, cudaEnableDefault, &qres));
+  if (!fn || qres != cudaDriverEntryPointSuccess) return BIKV_ERR_PEER;
+  unsigned long long base = 0;
+  size_t size = 0;
+  if (((get_range_fn)fn)(&base, &size, (unsigned long long)(uintptr_t)ptr) != 0) return BIKV_ERR_PEER;
+  cudaIpcMemHandle_t h;
+  cudaError_t e = cudaIpcGetMemHandle(&h, (void*)(uintptr_t)base);
+  if (e != cudaSuccess) {
+    cuda_fail(e);
+    return BIKV_ERR_PEER;
+  }
+  memcpy(handle, &h, 64);
+  *offset = (int64_t)((unsigned long long)(uintptr_t)ptr - base);
+  return BIKV_OK;
+}
+
+int bikv_pool_import(const unsigned char handle[64], int64_t offset, void** ptr) {
+  if (!handle || !ptr || offset < 0) return BIKV_ERR_BAD_ARG;
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, 64);
+  void* base = nullptr;
+  cudaError_t e = cudaIpcOpenMemHandle(&base, h, cudaIpcMemLazyEnablePeerAccess);
+  if (e != cudaSuccess) {
+    cuda_fail(e);
+    return BIKV_ERR_PEER;
+  }
+  *ptr = (char*)base + offset;
+  return BIKV_OK;
+}
+
+namespace {
+std::mutex g_imp_mu;
+}
+
+int bikv_pool_close(void* ptr) {
+  if (!ptr) return BIKV_ERR_BAD_ARG;
+  // cudaIpcCloseMemHandle wants the mapping's base: recover it the same way
+  // export does.
+  typedef int (*get_range_fn)(unsigned long long*, size_t*, unsigned long long);
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  BIKV_CUDA(cudaGetDriverEntryPoint("cuMemGetAddressRange", &fn, cudaEnableDefault, &qres));
+  if (!fn || qres != cudaDriverEntryPointSuccess) return BIKV_ERR_PEER;
+  unsigned long long base = 0;
+  size_t size = 0;
+  if (((get_range_fn)fn)(&base, &size, (unsigned long long)(uintptr_t)ptr) != 0) return BIKV_ERR_PEER;
+  std::lock_guard<std::mutex> lk(g_imp_mu);
+  BIKV_CUDA(cudaIpcCloseMemHandle((void*)(uintptr_t)base));
+  return BIKV_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,419 @@
+// Device code of the KV-page data path: pure data movement, no arithmetic.
+//
+// Three kernels cover the paged pool layout and the flat reference copy:
+//   k_paged_ldst   one warp per (page, plane, part) chunk, 16-byte ld/st
+//   k_paged_bulk   one issuing thread per CTA, cp.async.bulk ring
+//                  global -> shared -> global (no multicast, no tensor map)
+//   k_flat         dst[dst_off[i]+e] = src[src_off[i]+e], any alignment
+// and one covers the reference's token-major pool:
+//   k_token_major  shared-memory transpose of [dim][head][layer][kv] token rows
+//                  into [layer][kv][token][head][dim] (and back)
+//
+// A "plane" is one (layer, kv) pair; in the paged layout a page holds
+// 2*n_layers planes of page_tokens*heads*dim elements each, so a plane of a
+// page and its window in the worker tensor are both contiguous byte runs.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include "bikv.h"
+
+namespace bikv {
+
+struct PoolDev {
+  char* base[BIKV_MAX_SHARDS];
+  int n_shards;
+  int rule;
+  long long pages_per_shard;
+};
+
+struct PagedArgs {
+  const uint4* recs;               // bikv_page_rec viewed as 16-byte words
+  const bikv_request_desc* reqs;
+  PoolDev pool;
+  unsigned n_items;                // n_pages * planes * parts
+  unsigned planes;                 // 2 * n_layers
+  unsigned parts;                  // ceil(plane_bytes / seg_bytes)
+  unsigned seg_bytes;
+  unsigned row_bytes;              // heads * dim * elt_bytes (one token of one plane)
+  unsigned plane_bytes;            // page_tokens * row_bytes
+  unsigned long long page_bytes;   // planes * plane_bytes
+  int to_pool;                     // 0 = gather (pool -> worker), 1 = scatter
+  int* status;
+};
+
+__device__ __forceinline__ uint4 ld_stream16(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+__device__ __forceinline__ void st_stream16(void* p, const uint4& v) {
+  asm volatile("st.global.L1::no_allocate.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x),
+               "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+}
+
+// Resolves chunk w to (pool address, worker address, byte count).  Returns
+// false for a part that lies wholly beyond the valid tokens of a partial page.
+__device__ __forceinline__ bool decode_item(const PagedArgs& a, unsigned w, char*& pool_p,
+                                            char*& work_p, unsigned& bytes) {
+  const unsigned part = w % a.parts;
+  const unsigned t = w / a.parts;
+  const unsigned plane = t % a.planes;
+  const unsigned page = t / a.planes;
+  const uint4 r = __ldg(a.recs + page);
+  const unsigned vbytes = r.y * a.row_bytes;
+  const unsigned off = part * a.seg_bytes;
+  if (off >= vbytes) return false;
+  bytes = min(a.seg_bytes, vbytes - off);
+  const unsigned id = r.x;
+  unsigned shard;
+  unsigned long long local;
+  if (a.pool.rule == BIKV_SHARD_MOD) {
+    shard = id % (unsigned)a.pool.n_shards;
+    local = id / (unsigned)a.pool.n_shards;
+  } else {
+    shard = (unsigned)(id / a.pool.pages_per_shard);
+    local = id % a.pool.pages_per_shard;
+  }
+  pool_p = a.pool.base[shard] + local * a.page_bytes + (unsigned long long)plane * a.plane_bytes + off;
+  const longlong2 rq = __ldg(reinterpret_cast<const longlong2*>(a.reqs + r.z));
+  work_p = reinterpret_cast<char*>(rq.x) +
+           ((unsigned long long)plane * (unsigned long long)rq.y + r.w) * a.row_bytes + off;
+  return true;
+}
+
+// Copies `bytes` from src to dst with the 32 lanes of one warp.  Fast path:
+// both 16-byte aligned.  Otherwise the widest power-of-two unit that divides
+// both addresses is used, with a byte tail.
+template <int U>
+__device__ __forceinline__ void warp_copy(const char* src, char* dst, unsigned long long bytes,
+                                          int lane) {
+  const unsigned long long mis = (unsigned long long)src | (unsigned long long)dst;
+  if ((mis & 15) == 0) {
+    const uint4* s = reinterpret_cast<const uint4*>(src);
+    uint4* d = reinterpret_cast<uint4*>(dst);
+    const unsigned long long n = bytes >> 4;
+    unsigned long long i = lane;
+    for (; i + 32ull * (U - 1) < n; i += 32ull * U) {
+      uint4 v[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) v[u] = ld_stream16(s + i + 32 * u);
+#pragma unroll
+      for (int u = 0; u < U; ++u) st_stream16(d + i + 32 * u, v[u]);
+    }
+    for (; i < n; i += 32) st_stream16(d + i, ld_stream16(s + i));
+    for (unsigned long long b = (n << 4) + lane; b < bytes; b += 32) dst[b] = src[b];
+    return;
+  }
+  if (((unsigned long long)src & 15) == ((unsigned long long)dst & 15)) {
+    // Same misalignment on both sides: peel a byte head, then the fast path.
+    unsigned long long head = 16 - ((unsigned long long)src & 15);
+    if (head > bytes) head = bytes;
+    for (unsigned long long b = lane; b < head; b += 32) dst[b] = src[b];
+    if (bytes > head) warp_copy<U>(src + head, dst + head, bytes - head, lane);
+    return;
+  }
+  if ((mis & 7) == 0) {
+    const unsigned long long n = bytes >> 3;
+    for (unsigned long long i = lane; i < n; i += 32)
+      reinterpret_cast<unsigned long long*>(dst)[i] = reinterpret_cast<const unsigned long long*>(src)[i];
+    for (unsigned long long b = (n << 3) + lane; b < bytes; b += 32) dst[b] = src[b];
+  } else if ((mis & 3) == 0) {
+    const unsigned long long n = bytes >> 2;
+    for (unsigned long long i = lane; i < n; i += 32)
+      reinterpret_cast<unsigned*>(dst)[i] = reinterpret_cast<const unsigned*>(src)[i];
+    for (unsigned long long b = (n << 2) + lane; b < bytes; b += 32) dst[b] = src[b];
+  } else if ((mis & 1) == 0) {
+    const unsigned long long n = bytes >> 1;
+    for (unsigned long long i = lane; i < n; i += 32)
+      reinterpret_cast<unsigned short*>(dst)[i] = reinterpret_cast<const unsigned short*>(src)[i];
+    for (unsigned long long b = (n << 1) + lane; b < bytes; b += 32) dst[b] = src[b];
+  } else {
+    for (unsigned long long b = lane; b < bytes; b += 32) dst[b] = src[b];
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Paged layout, direct ld/st.  Adjacent warps take adjacent planes of a page,
+// so a CTA reads one contiguous stretch of the pool page per sweep.
+// ---------------------------------------------------------------------------
+template <int U>
+__global__ void __launch_bounds__(256) k_paged_ldst(const __grid_constant__ PagedArgs a) {
+  const int lane = threadIdx.x & 31;
+  const unsigned warps_per_cta = blockDim.x >> 5;
+  const unsigned stride = gridDim.x * warps_per_cta;
+  for (unsigned w = blockIdx.x * warps_per_cta + (threadIdx.x >> 5); w < a.n_items; w += stride) {
+    char *pool_p, *work_p;
+    unsigned bytes;
+    if (!decode_item(a, w, pool_p, work_p, bytes)) continue;
+    if (a.to_pool)
+      warp_copy<U>(work_p, pool_p, bytes, lane);
+    else
+      warp_copy<U>(pool_p, work_p, bytes, lane);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Paged layout, bulk-async ring.  Thread 0 of each CTA runs a software
+// pipeline over `stages` shared-memory buffers of seg_bytes each:
+//   load(k+stages-1) in flight | wait full(k) | store(k) | refill stage of k-1
+// Every wait on an mbarrier is bounded; on expiry the thread records
+// BIKV_ERR_DEVICE_TIMEOUT in status[0], stops issuing, drains its stores and
+// gives every outstanding load one more bounded wait before returning.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait: at most ~2 s of wall time and at most 2^24 polls.
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long deadline = global_timer_ns() + 2000000000ull;
+  for (unsigned i = 0; i < (1u << 24); ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 63) == 63 && global_timer_ns() > deadline) break;
+  }
+  return false;
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst_smem, const void* src, uint32_t bytes,
+                                         uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst_smem),
+      "l"(src), "r"(bytes), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void bulk_s2g(void* dst, uint32_t src_smem, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst),
+               "r"(src_smem), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read_1() {
+  asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+}
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
+constexpr int kMaxStages = 12;
+
+__global__ void __launch_bounds__(32) k_paged_bulk(const __grid_constant__ PagedArgs a, int stages) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  __shared__ __align__(8) unsigned long long bars[kMaxStages];
+  if (threadIdx.x != 0) return;
+
+  for (int s = 0; s < stages; ++s) mbar_init(smem_u32(&bars[s]), 1);
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+
+  const uint32_t buf0 = smem_u32(smem);
+  const unsigned stride = gridDim.x;
+  // Number of chunks this CTA owns: w = blockIdx.x + k*stride.
+  const unsigned mine = (a.n_items > blockIdx.x) ? (a.n_items - blockIdx.x + stride - 1) / stride : 0;
+
+  unsigned phase_bits = 0;      // bit s = parity to wait for on stage s
+  unsigned loaded_bits = 0;     // bit s = a load is outstanding on stage s
+  // Per-stage destination and size of the chunk held there.
+  char* st_dst[kMaxStages];
+  unsigned st_bytes[kMaxStages];
+  bool failed = false;
+
+  auto issue_load = [&](unsigned k) {
+    const int s = k % stages;
+    char *pool_p, *work_p;
+    unsigned bytes;
+    st_bytes[s] = 0;
+    if (k >= mine) return;
+    if (!decode_item(a, blockIdx.x + k * stride, pool_p, work_p, bytes)) return;
+    const char* src = a.to_pool ? work_p : pool_p;
+    st_dst[s] = a.to_pool ? pool_p : work_p;
+    st_bytes[s] = bytes;
+    const uint32_t bar = smem_u32(&bars[s]);
+    mbar_expect_tx(bar, bytes);
+    bulk_g2s(buf0 + s * a.seg_bytes, src, bytes, bar);
+    loaded_bits |= 1u << s;
+  };
+
+  for (unsigned k = 0; k + 1 < (unsigned)stages && k < mine; ++k) issue_load(k);
+
+  for (unsigned k = 0; k < mine; ++k) {
+    const int s = k % stages;
+    if (st_bytes[s] != 0) {
+      if (!mbar_wait_bounded(smem_u32(&bars[s]), (phase_bits >> s) & 1)) {
+        failed = true;
+        break;
+      }
+      phase_bits ^= 1u << s;
+      loaded_bits &= ~(1u << s);
+      bulk_s2g(st_dst[s], buf0 + s * a.seg_bytes, st_bytes[s]);
+    }
+    bulk_commit();
+    // The store of chunk k-1 has finished reading its stage once at most one
+    // group (the one just committed) is still pending; that stage is the one
+    // chunk k+stages-1 maps to.
+    bulk_wait_read_1();
+    issue_load(k + stages - 1);
+  }
+
+  bulk_wait_all();
+  if (failed) {
+    if (a.status) atomicExch(a.status, (int)BIKV_ERR_DEVICE_TIMEOUT);
+    for (int s = 0; s < stages; ++s)
+      if (loaded_bits & (1u << s)) (void)mbar_wait_bounded(smem_u32(&bars[s]), (phase_bits >> s) & 1);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Flat page copy (reference kernel semantics).  One warp per (page, part).
+// ---------------------------------------------------------------------------
+struct FlatArgs {
+  const char* src;
+  char* dst;
+  const long long* src_off;  // elements; may be null (all zero)
+  const long long* dst_off;
+  unsigned long long page_bytes;
+  unsigned long long n_items;  // n_pages * parts
+  unsigned parts;
+  unsigned seg_bytes;
+  unsigned elt_bytes;
+};
+
+template <int U>
+__global__ void __launch_bounds__(256) k_flat(const __grid_constant__ FlatArgs a) {
+  const int lane = threadIdx.x & 31;
+  const unsigned warps_per_cta = blockDim.x >> 5;
+  const unsigned long long stride = (unsigned long long)gridDim.x * warps_per_cta;
+  for (unsigned long long w = (unsigned long long)blockIdx.x * warps_per_cta + (threadIdx.x >> 5);
+       w < a.n_items; w += stride) {
+    const unsigned part = (unsigned)(w % a.parts);
+    const unsigned long long page = w / a.parts;
+    const unsigned long long off = (unsigned long long)part * a.seg_bytes;
+    unsigned long long bytes = a.page_bytes - off;
+    if (bytes > a.seg_bytes) bytes = a.seg_bytes;
+    const long long so = a.src_off ? __ldg(a.src_off + page) : 0;
+    const long long dn = a.dst_off ? __ldg(a.dst_off + page) : 0;
+    warp_copy<U>(a.src + so * (long long)a.elt_bytes + off, a.dst + dn * (long long)a.elt_bytes + off,
+                 bytes, lane);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Token-major (reference) pool <-> layer-major worker KV.
+//
+// Pool token row: element (d, h, c) at ((d*H + h)*C + c), c = layer*2 + kv,
+// C = 2*n_layers.  Worker: element (c, tok, h, d) at ((c*T + tok)*H + h)*D + d.
+// A CTA stages a slab of DT consecutive d (all heads, all planes) of one token
+// in shared memory: the pool side of the slab is one contiguous run and moves
+// with 16-byte accesses; the worker side moves as 16-byte vectors of V = 16/elt
+// consecutive d for a fixed (c, h).  Lanes vary c fastest so the element-wise
+// shared-memory accesses of a warp fall on consecutive addresses.
+// ---------------------------------------------------------------------------
+struct TokenMajorArgs {
+  const uint4* recs;
+  const bikv_request_desc* reqs;
+  PoolDev pool;
+  unsigned n_items;       // n_pages * page_tokens * slabs
+  unsigned page_tokens;
+  unsigned slabs;         // D / DT
+  unsigned DT;            // d per slab (multiple of V)
+  unsigned H, D, C;
+  unsigned long long token_bytes;  // D*H*C*elt
+  int to_pool;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256) k_token_major(const __grid_constant__ TokenMajorArgs a) {
+  extern __shared__ __align__(16) unsigned char tm_smem[];
+  T* tile = reinterpret_cast<T*>(tm_smem);
+  constexpr unsigned V = 16 / sizeof(T);
+  const unsigned slab_elems = a.DT * a.H * a.C;
+  const unsigned slab_vec = slab_elems / V;       // slab bytes / 16
+  const unsigned groups = a.DT / V;               // d-groups per slab
+  const unsigned n_out = a.C * a.H * groups;      // 16-byte worker vectors per slab
+
+  for (unsigned w = blockIdx.x; w < a.n_items; w += gridDim.x) {
+    const unsigned slab = w % a.slabs;
+    const unsigned t = w / a.slabs;
+    const unsigned tok = t % a.page_tokens;
+    const unsigned page = t / a.page_tokens;
+    const uint4 r = __ldg(a.recs + page);
+    if (tok >= r.y) continue;  // uniform across the CTA
+    const unsigned id = r.x;
+    unsigned shard;
+    unsigned long long local;
+    if (a.pool.rule == BIKV_SHARD_MOD) {
+      shard = id % (unsigned)a.pool.n_shards;
+      local = id / (unsigned)a.pool.n_shards;
+    } else {
+      shard = (unsigned)(id / a.pool.pages_per_shard);
+      local = id % a.pool.pages_per_shard;
+    }
+    char* pool_p = a.pool.base[shard] + (local * a.page_tokens + tok) * a.token_bytes +
+                   (unsigned long long)slab * slab_elems * sizeof(T);
+    const longlong2 rq = __ldg(reinterpret_cast<const longlong2*>(a.reqs + r.z));
+    T* work = reinterpret_cast<T*>(rq.x);
+    const unsigned long long T_req = (unsigned long long)rq.y;
+    const unsigned long long wtok = r.w + tok;
+    const unsigned d_base = slab * a.DT;
+
+    if (!a.to_pool) {
+      const uint4* s = reinterpret_cast<const uint4*>(pool_p);
+      uint4* d = reinterpret_cast<uint4*>(tile);
+      for (unsigned i = threadIdx.x; i < slab_vec; i += blockDim.x) d[i] = ld_stream16(s + i);
+      __syncthreads();
+      for (unsigned o = threadIdx.x; o < n_out; o += blockDim.x) {
+        const unsigned c = o % a.C;
+        const unsigned q = o / a.C;
+        const unsigned h = q % a.H;
+        const unsigned g = q / a.H;
+        union { uint4 v; T e[V]; } u;
+#pragma unroll
+        for (unsigned j = 0; j < V; ++j) u.e[j] = tile[((g * V + j) * a.H + h) * a.C + c];
+        T* dst = work + ((c * T_req + wtok) * a.H + h) * a.D + d_base + g * V;
+        st_stream16(dst, u.v);
+      }
+      __syncthreads();
+    } else {
+      for (unsigned o = threadIdx.x; o < n_out; o += blockDim.x) {
+        const unsigned c = o % a.C;
+        const unsigned q = o / a.C;
+        const unsigned h = q % a.H;
+        const unsigned g = q / a.H;
+        union { uint4 v; T e[V]; } u;
+        const T* src = work + ((c * T_req + wtok) * a.H + h) * a.D + d_base + g * V;
+        u.v = ld_stream16(src);
+#pragma unroll
+        for (unsigned j = 0; j < V; ++j) tile[((g * V + j) * a.H + h) * a.C + c] = u.e[j];
+      }
+      __syncthreads();
+      const uint4* s = reinterpret_cast<const uint4*>(tile);
+      uint4* d = reinterpret_cast<uint4*>(pool_p);
+      for (unsigned i = threadIdx.x; i < slab_vec; i += blockDim.x) st_stream16(d + i, s[i]);
+      __syncthreads();
+    }
+  }
+}
+
+}  // namespace bikv

@@ -1,0 +1,141 @@
+"""PageMover: launches gather / scatter for one worker GPU.
+
+Owns the small device-side state the C ABI leaves to the caller: the status
+words a kernel's bounded wait reports into, and the device staging buffer a
+host-resident plan is uploaded to.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional, Sequence, Union
+
+import numpy as np
+import torch
+
+from . import _native as N
+from .geometry import KVGeometry
+from .plan import Plan
+from .pool import ShardedPool
+
+Tensors = Union[torch.Tensor, Sequence[torch.Tensor]]
+
+
+class PageMover:
+    def __init__(self, device=None, variant: int = N.VARIANT_AUTO):
+        if not torch.cuda.is_available():
+            raise RuntimeError("PageMover needs a CUDA device: the KV-page path has no CPU implementation")
+        N.lib()  # fail now, loudly, if the library is missing
+        self.device = torch.device(device if device is not None else f"cuda:{torch.cuda.current_device()}")
+        self.variant = variant
+        self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
+        self._scratch = torch.empty(1 << 20, dtype=torch.uint8, device=self.device)
+        self._req_cap = 0
+        self._req_host: Optional[torch.Tensor] = None
+
+    # -- helpers -----------------------------------------------------------
+    def _stream(self, stream) -> int:
+        s = stream if stream is not None else torch.cuda.current_stream(self.device)
+        return int(s.cuda_stream)
+
+    def _scratch_for(self, n_pages: int, n_requests: int) -> torch.Tensor:
+        need = N.lib().bikv_plan_scratch_bytes(n_pages, n_requests)
+        if self._scratch.numel() < need:
+            self._scratch = torch.empty(int(need * 1.5), dtype=torch.uint8, device=self.device)
+        return self._scratch
+
+    def request_table(self, geom: KVGeometry, tensors: Tensors) -> torch.Tensor:
+        """Host (pinned) int64 [n, 2] table of (base pointer, tokens) for worker tensors
+        of shape ``geom.worker_shape(T)``."""
+        ts = [tensors] if isinstance(tensors, torch.Tensor) else list(tensors)
+        n = len(ts)
+        if self._req_host is None or self._req_cap < n:
+            self._req_cap = max(n, 64)
+            self._req_host = torch.empty((self._req_cap, 2), dtype=torch.int64).pin_memory()
+        tab = self._req_host.numpy()
+        L, H, D = geom.n_layers, geom.n_kv_heads, geom.head_dim
+        for i, t in enumerate(ts):
+            if t.dim() != 5 or t.shape[0] != L or t.shape[1] != 2 or t.shape[3] != H or t.shape[4] != D:
+                raise ValueError(f"worker tensor {i} has shape {tuple(t.shape)}, want {geom.worker_shape('T')}")
+            if not t.is_contiguous() or t.element_size() != geom.elt_bytes:
+                raise ValueError(f"worker tensor {i} must be contiguous with {geom.elt_bytes}-byte elements")
+            if t.device != self.device:
+                raise ValueError(f"worker tensor {i} lives on {t.device}, mover on {self.device}")
+            tab[i, 0] = t.data_ptr()
+            tab[i, 1] = t.shape[2]
+        return self._req_host[:n]
+
+    # -- host-plan path ----------------------------------------------------
+    def _run_h(self, fn, pool: ShardedPool, plan: Plan, tensors: Tensors, validate: bool,
+               variant: Optional[int], stream) -> None:
+        if plan.n_pages == 0:
+            return
+        reqs = self.request_table(pool.geom, tensors)
+        if len(reqs) < plan.n_requests:
+            raise ValueError(f"plan names {plan.n_requests} worker tensors, {len(reqs)} given")
+        scratch = self._scratch_for(plan.n_pages, len(reqs))
+        g = pool.geom.native()
+        rc = fn(C.byref(pool.desc), C.byref(g), C.c_void_p(plan.host_ptr), plan.n_pages,
+                C.c_void_p(reqs.data_ptr()), len(reqs), C.c_void_p(scratch.data_ptr()),
+                scratch.numel(), int(validate), self.variant if variant is None else variant,
+                C.c_void_p(self.status.data_ptr()), C.c_void_p(self._stream(stream)))
+        N.check(rc, fn.__name__)
+
+    def gather(self, pool: ShardedPool, plan: Plan, tensors: Tensors, *, validate: bool = True,
+               variant: Optional[int] = None, stream=None) -> None:
+        """Pool pages -> worker tensors (``[layer, kv, token, head, dim]``), asynchronously."""
+        self._run_h(N.lib().bikv_gather_h, pool, plan, tensors, validate, variant, stream)
+
+    def scatter(self, pool: ShardedPool, plan: Plan, tensors: Tensors, *, validate: bool = True,
+                variant: Optional[int] = None, stream=None) -> None:
+        """Worker tensors -> pool pages (inverse map of :meth:`gather`)."""
+        self._run_h(N.lib().bikv_scatter_h, pool, plan, tensors, validate, variant, stream)
+
+    # -- device-plan path --------------------------------------------------
+    def upload(self, plan: Plan, geom: KVGeometry, tensors: Tensors):
+        """Copies a plan and its request table to fresh device tensors (for repeated
+        launches of one plan)."""
+        recs = torch.from_numpy(np.ascontiguousarray(plan.table)).to(self.device)
+        reqs = self.request_table(geom, tensors).to(self.device)
+        return recs, reqs
+
+    def _run_d(self, fn, pool: ShardedPool, recs: torch.Tensor, reqs: torch.Tensor,
+               variant: Optional[int], stream) -> None:
+        g = pool.geom.native()
+        rc = fn(C.byref(pool.desc), C.byref(g), C.c_void_p(recs.data_ptr()), recs.shape[0],
+                C.c_void_p(reqs.data_ptr()), reqs.shape[0], self.variant if variant is None else variant,
+                C.c_void_p(self.status.data_ptr()), C.c_void_p(self._stream(stream)))
+        N.check(rc, fn.__name__)
+
+    def gather_dev(self, pool, recs, reqs, *, variant=None, stream=None) -> None:
+        self._run_d(N.lib().bikv_gather, pool, recs, reqs, variant, stream)
+
+    def scatter_dev(self, pool, recs, reqs, *, variant=None, stream=None) -> None:
+        self._run_d(N.lib().bikv_scatter, pool, recs, reqs, variant, stream)
+
+    # -- flat copy ---------------------------------------------------------
+    def copy_pages_flat(self, src: torch.Tensor, dst: torch.Tensor, src_off: torch.Tensor,
+                        dst_off: torch.Tensor, page_elems: int, *, stream=None) -> None:
+        """``dst[dst_off[i]+e] = src[src_off[i]+e]`` for ``e < page_elems`` (element offsets)."""
+        if src_off.dtype != torch.int64 or dst_off.dtype != torch.int64:
+            raise TypeError("offsets must be int64")
+        if src_off.shape != dst_off.shape:
+            raise ValueError("offset arrays differ in length")
+        rc = N.lib().bikv_copy_pages_flat(C.c_void_p(src.data_ptr()), C.c_void_p(dst.data_ptr()),
+                                          C.c_void_p(src_off.data_ptr()), C.c_void_p(dst_off.data_ptr()),
+                                          src_off.numel(), int(page_elems), src.element_size(),
+                                          C.c_void_p(self._stream(stream)))
+        N.check(rc, "bikv_copy_pages_flat")
+
+    def copy_range(self, dst_ptr: int, src_ptr: int, nbytes: int, *, stream=None) -> None:
+        rc = N.lib().bikv_copy_range(C.c_void_p(dst_ptr), C.c_void_p(src_ptr), int(nbytes),
+                                     C.c_void_p(self._stream(stream)))
+        N.check(rc, "bikv_copy_range")
+
+    # -- status ------------------------------------------------------------
+    def check_status(self) -> None:
+        """Synchronising read of the device status words; raises if a kernel's bounded
+        wait ran out, and clears the words."""
+        st = self.status.cpu()
+        if int(st[0]) != 0:
+            self.status.zero_()
+            raise N.BikvError(int(st[0]), "device status")

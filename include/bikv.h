@@ -1,0 +1,245 @@
+/*
+ * bikv.h -- C ABI of the B200 KV-page data path (libbikv.so).
+ *
+ * The library moves KV-cache pages between sharded page pools (the KVCache
+ * shards of Bi-KV) and a worker's contiguous per-request KV tensors:
+ *
+ *   gather   pool pages  -> worker KV   (task type SEND in the reference)
+ *   scatter  worker KV   -> pool pages  (task type RECV in the reference)
+ *
+ * Everything crosses this boundary as plain pointers and sizes; no torch or
+ * C++ types appear.  All device work is asynchronous on the stream the caller
+ * passes (a cudaStream_t cast to void*; NULL is the legacy default stream).
+ * Unless a function says otherwise the library allocates no device memory and
+ * never frees caller memory.
+ *
+ * Each entry point names the reference interface it replaces, as
+ * path:line inside the Bi-KV project.
+ */
+#ifndef BIKV_H_
+#define BIKV_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define BIKV_ABI_VERSION 1
+#define BIKV_MAX_SHARDS 16
+
+/* ---- status codes (0 = success, negative = error) ----------------------- */
+enum bikv_status {
+  BIKV_OK = 0,
+  BIKV_ERR_BAD_ARG = -1,        /* null pointer, non-positive size, unknown enum        */
+  BIKV_ERR_PAGE_RANGE = -2,     /* page id outside the pool                              */
+  BIKV_ERR_DST_RANGE = -3,      /* token window outside the request's KV tensor          */
+  BIKV_ERR_ALIGNMENT = -4,      /* a base or a row is not 16-byte aligned                */
+  BIKV_ERR_PEER = -5,           /* peer access / IPC mapping could not be set up         */
+  BIKV_ERR_CUDA = -6,           /* a CUDA call failed; see bikv_last_cuda_error()        */
+  BIKV_ERR_OVERLAP = -7,        /* two records of a scatter plan write the same page     */
+  BIKV_ERR_DEVICE_TIMEOUT = -8, /* a bounded wait inside a kernel ran out                */
+  BIKV_ERR_TOO_LARGE = -9,      /* plan or size beyond a documented maximum              */
+  BIKV_ERR_PLAN = -10           /* plan inconsistent (page count vs token count, ...)    */
+};
+
+/* ---- pool page layouts --------------------------------------------------- */
+enum bikv_pool_layout {
+  /* page = [layer][kv][page_token][head][dim]; every (page, layer, kv) plane
+   * is one contiguous run of page_tokens*heads*dim elements.               */
+  BIKV_POOL_PAGED = 0,
+  /* The reference pool: page = page_tokens consecutive tokens, each token
+   * laid out [dim][head][layer][kv] (DistributedStorage/kvcache.py:38-43 with
+   * token_shape of Model/qwen2.py:519-522).                                 */
+  BIKV_POOL_TOKEN_MAJOR = 1
+};
+
+/* How a global page id maps to (shard, page inside the shard). */
+enum bikv_shard_rule {
+  BIKV_SHARD_MOD = 0,   /* shard = id % n_shards, local = id / n_shards                */
+  BIKV_SHARD_BLOCK = 1  /* shard = id / pages_per_shard, local = id % pages_per_shard
+                           (the reference's item-granular placement: id =
+                           cache_worker * pages_per_shard + page)                      */
+};
+
+/* Copy engine selection for the paged layout. */
+enum bikv_variant {
+  BIKV_VARIANT_AUTO = 0,
+  BIKV_VARIANT_LDST = 1, /* warp per chunk, 16-byte ld/st                              */
+  BIKV_VARIANT_BULK = 2  /* cp.async.bulk global->shared->global ring per CTA          */
+};
+
+typedef struct bikv_geometry {
+  int32_t n_layers;
+  int32_t n_kv_heads;
+  int32_t head_dim;
+  int32_t page_tokens;
+  int32_t elt_bytes;   /* 2 for fp16 / bf16 (bit passthrough), 1 and 4 also accepted */
+  int32_t pool_layout; /* enum bikv_pool_layout */
+} bikv_geometry;
+
+/* One page of a plan.  `request` selects the worker KV tensor, `token_offset`
+ * the first token inside it, `valid_tokens` (1..page_tokens) how many tokens of
+ * the page carry data (a request's last page may be partial). */
+typedef struct bikv_page_rec {
+  int32_t page_id;
+  int32_t valid_tokens;
+  int32_t request;
+  int32_t token_offset;
+} bikv_page_rec;
+
+/* A worker-side KV tensor, layout [layer][kv][tokens][head][dim]. */
+typedef struct bikv_request_desc {
+  void* base;
+  int64_t tokens;
+} bikv_request_desc;
+
+/* The sharded pool as one worker GPU sees it: shard_base[s] is a device pointer
+ * valid on the calling GPU (its own memory, or a peer mapping). */
+typedef struct bikv_pool_desc {
+  void* shard_base[BIKV_MAX_SHARDS];
+  int32_t n_shards;
+  int32_t shard_rule; /* enum bikv_shard_rule */
+  int64_t pages_per_shard;
+} bikv_pool_desc;
+
+/* ---- library ------------------------------------------------------------- */
+int bikv_version(void);
+const char* bikv_strerror(int status);
+/* cudaError_t of the last failing CUDA call on this thread (0 if none). */
+int bikv_last_cuda_error(void);
+/* Number of kernels this library has launched in this process. */
+int64_t bikv_launch_count(void);
+/* Tuning knobs: "ldst_ctas_per_sm", "bulk_ctas_per_sm", "bulk_stages",
+ * "seg_bytes", "auto_variant".  Returns BIKV_ERR_BAD_ARG for unknown names or
+ * values out of range. */
+int bikv_set_tuning(const char* name, int64_t value);
+int64_t bikv_get_tuning(const char* name);
+
+/* ---- plan (host) --------------------------------------------------------- */
+/*
+ * Builds page records from a coordinator plan.  Replaces the index loops of
+ * KVCache.shared_data_batch_pages (DistributedStorage/kvcache.py:158-196):
+ * items are walked in order, each page of an item gets the running token
+ * offset of its request, and the last page of an item whose token count is
+ * not a multiple of page_tokens carries only the remainder.
+ *   pages_flat      all items' page ids, concatenated
+ *   item_page_begin n_items+1 offsets into pages_flat
+ *   item_tokens     token count per item
+ *   item_request    destination tensor per item, or NULL (all request 0)
+ *   item_shard      cache_worker per item for BIKV_SHARD_BLOCK (page id becomes
+ *                   shard*pages_per_shard + page), or NULL
+ *   request_tokens  in/out: running token count per request (start at 0)
+ * Returns the number of records written (>= 0) or a negative status.
+ */
+int64_t bikv_plan_build(const int32_t* pages_flat, const int64_t* item_page_begin,
+                        const int32_t* item_tokens, const int32_t* item_request,
+                        const int32_t* item_shard, int64_t pages_per_shard,
+                        int32_t n_items, int32_t page_tokens,
+                        int64_t* request_tokens, int32_t n_requests,
+                        bikv_page_rec* out, int64_t out_capacity);
+
+/*
+ * Checks a host-resident plan before anything is launched: page ids inside the
+ * pool, valid_tokens in 1..page_tokens, token windows inside their request,
+ * geometry sane, and (check_overlap != 0) no pool page named twice -- required
+ * for scatter.  The reference performs no such check (copy_kernel.cu:68-129
+ * launches unconditionally).  request_base may be NULL (alignment unchecked).
+ */
+int bikv_plan_validate(const bikv_page_rec* recs, int64_t n_pages,
+                       const bikv_request_desc* requests, int32_t n_requests,
+                       const bikv_pool_desc* pool, const bikv_geometry* geom,
+                       int check_overlap);
+
+/* ---- gather / scatter (device) ------------------------------------------- */
+/*
+ * Gather: for every record, pool page -> request KV window, converting the pool
+ * layout into [layer][kv][tokens][head][dim].  Replaces
+ * cuda_producer_copy_pages + block_per_page_copy_kernel
+ * (SharedMemory/CUDA_Shared/copy_kernel.cu:10-36,68-129) and, when a shard base
+ * is a peer mapping, the one-sided read of NetworkTransport/onesided_rdma.h:706-759.
+ *   recs_dev / requests_dev  device arrays (n_pages / n_requests entries)
+ *   status_dev               device int32[4], zeroed by the caller; word 0
+ *                            receives a bikv_status if a bounded device wait
+ *                            runs out.  May be NULL for BIKV_VARIANT_LDST.
+ */
+int bikv_gather(const bikv_pool_desc* pool, const bikv_geometry* geom,
+                const bikv_page_rec* recs_dev, int64_t n_pages,
+                const bikv_request_desc* requests_dev, int32_t n_requests,
+                int variant, int32_t* status_dev, void* stream);
+
+/*
+ * Scatter: the exact inverse index map of bikv_gather (request KV window ->
+ * pool page; only valid_tokens tokens of a partial page are written).  The
+ * reference has no kernel for this direction; it is implied by
+ * KVCache.receive_data_batch (DistributedStorage/kvcache.py:116-130) and
+ * Worker.send_kvcache_data_batch (Worker/Worker.py:193-218), and by the
+ * one-sided write of NetworkTransport/onesided_rdma.h:652-704.
+ */
+int bikv_scatter(const bikv_pool_desc* pool, const bikv_geometry* geom,
+                 const bikv_page_rec* recs_dev, int64_t n_pages,
+                 const bikv_request_desc* requests_dev, int32_t n_requests,
+                 int variant, int32_t* status_dev, void* stream);
+
+/*
+ * Host-plan forms: the plan lives in host memory (pinned for a truly
+ * asynchronous upload).  The call validates it (validate != 0), copies it into
+ * `plan_scratch_dev` (caller-owned device memory of at least
+ * bikv_plan_scratch_bytes(n_pages, n_requests) bytes) on `stream`, and launches
+ * the kernel behind it.  This is what KVCache.send_data_batch /
+ * receive_data_batch (DistributedStorage/kvcache.py:96-130) call.
+ * The host arrays must stay unchanged until the stream has passed the upload.
+ */
+int64_t bikv_plan_scratch_bytes(int64_t n_pages, int32_t n_requests);
+int bikv_gather_h(const bikv_pool_desc* pool, const bikv_geometry* geom,
+                  const bikv_page_rec* recs_host, int64_t n_pages,
+                  const bikv_request_desc* requests_host, int32_t n_requests,
+                  void* plan_scratch_dev, int64_t plan_scratch_bytes, int validate,
+                  int variant, int32_t* status_dev, void* stream);
+int bikv_scatter_h(const bikv_pool_desc* pool, const bikv_geometry* geom,
+                   const bikv_page_rec* recs_host, int64_t n_pages,
+                   const bikv_request_desc* requests_host, int32_t n_requests,
+                   void* plan_scratch_dev, int64_t plan_scratch_bytes, int validate,
+                   int variant, int32_t* status_dev, void* stream);
+
+/*
+ * Flat page copy with the reference kernel's exact semantics
+ * (SharedMemory/CUDA_Shared/copy_kernel.cu:10-36): for every page i and element
+ * e < page_elems, dst[dst_off[i] + e] = src[src_off[i] + e]; offsets are in
+ * ELEMENTS of elt_bytes.  `src` may be device memory (producer_copy_pages,
+ * ipc_service.cpp:205-221) or pinned, device-mapped host memory
+ * (zero_copy_page_kernel, copy_kernel.cu:39-66).  Offsets are device arrays.
+ */
+int bikv_copy_pages_flat(const void* src, void* dst, const int64_t* src_off_dev,
+                         const int64_t* dst_off_dev, int64_t n_pages,
+                         int64_t page_elems, int32_t elt_bytes, void* stream);
+
+/*
+ * One contiguous byte range, device to device (either side may be a peer
+ * mapping).  Mirrors RDMAOneSidedEndpoint.post_rdma_write / post_rdma_read
+ * (NetworkTransport/onesided_rdma.h:652-759) without the completion poll: the
+ * copy is ordered on `stream`.
+ */
+int bikv_copy_range(void* dst, const void* src, int64_t bytes, void* stream);
+
+/* ---- peer mapping -------------------------------------------------------- */
+/* cudaDeviceCanAccessPeer / cudaDeviceEnablePeerAccess for in-process pools;
+ * already-enabled is success. */
+int bikv_can_access_peer(int device, int peer, int* can);
+int bikv_enable_peer(int device, int peer);
+/*
+ * Cross-process exposure of a shard pool, the role of consumer_init /
+ * producer_init (SharedMemory/CUDA_Shared/ipc_service.cpp:20-110) without the
+ * POSIX shm block or the staging ring: export yields the 64-byte CUDA IPC
+ * handle of the allocation that contains `ptr` plus ptr's offset inside it;
+ * import maps it in another process and returns the mapped address of `ptr`.
+ * bikv_pool_close takes the pointer import returned.
+ */
+int bikv_pool_export(void* ptr, unsigned char handle[64], int64_t* offset);
+int bikv_pool_import(const unsigned char handle[64], int64_t offset, void** ptr);
+int bikv_pool_close(void* ptr);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BIKV_H_ */

@@ -1,0 +1,245 @@
+"""Parity of the CUDA path (through the C ABI) with the CPU oracle: bit-exact."""
+import numpy as np
+import pytest
+import torch
+
+import bikv_b200 as B
+from bikv_b200 import _native as N
+from bikv_b200 import workloads as W
+from bikv_b200.geometry import KVGeometry
+from bikv_b200.plan import Plan, build_plan
+from oracle import bikv_oracle as O
+
+from helpers import equal_bits, make_shards, make_workers, random_plan
+
+pytestmark = pytest.mark.gpu
+
+TINY = KVGeometry(2, 1, 8, 4, torch.float16)            # 16-byte rows
+SMALL = KVGeometry(3, 2, 64, 16, torch.bfloat16)
+GEOS = {"tiny": TINY, "small": SMALL, "A": B.GEO_A, "B": B.GEO_B,
+        "C-lite": KVGeometry(4, 8, 128, 16, torch.float16),   # 32 KiB planes -> 2 parts
+        "u8": KVGeometry(2, 2, 32, 8, torch.uint8), "f32": KVGeometry(2, 2, 16, 8, torch.float32)}
+VARIANTS = {"ldst": N.VARIANT_LDST, "bulk": N.VARIANT_BULK}
+
+
+def run_case(cuda, geom, n_shards, pages_per_shard, n_requests, max_tokens, variant, rule=N.SHARD_MOD,
+             seed=0, fill="bits", min_tokens=1):
+    rng = np.random.default_rng(seed)
+    lists, tokens = random_plan(rng, geom, n_shards * pages_per_shard, n_requests, max_tokens, min_tokens)
+    plan = build_plan([l.tolist() for l in lists], tokens.astype(np.int32), geom.page_tokens,
+                      item_request=np.arange(n_requests, dtype=np.int32), n_requests=n_requests)
+    recs = [tuple(r) for r in plan.table.tolist()]
+    shards_cpu = make_shards(geom, n_shards, pages_per_shard, seed, fill=fill)
+    mover = B.PageMover(cuda)
+
+    # gather
+    shards_gpu = [s.to(cuda) for s in shards_cpu]
+    pool = B.ShardedPool.from_tensors(shards_gpu, geom, rule=rule)
+    out_gpu = make_workers(geom, tokens, cuda)
+    mover.gather(pool, plan, out_gpu, variant=variant)
+    out_cpu = make_workers(geom, tokens)
+    O.gather(shards_cpu, geom, recs, out_cpu, rule)
+    torch.cuda.synchronize()
+    mover.check_status()
+    for a, b in zip(out_gpu, out_cpu):
+        assert equal_bits(a, b)
+    for a, b in zip(shards_gpu, shards_cpu):
+        assert equal_bits(a, b), "gather must not write the pool"
+
+    # scatter fresh worker data into the pool
+    src_cpu = make_workers(geom, tokens, fill="normal", seed=seed + 1000)
+    src_gpu = [t.to(cuda) for t in src_cpu]
+    mover.scatter(pool, plan, src_gpu, variant=variant)
+    O.scatter(shards_cpu, geom, recs, src_cpu, rule)
+    torch.cuda.synchronize()
+    mover.check_status()
+    for a, b in zip(shards_gpu, shards_cpu):
+        assert equal_bits(a, b)
+    for a, b in zip(src_gpu, src_cpu):
+        assert equal_bits(a, b), "scatter must not write the worker tensors"
+
+
+@pytest.mark.parametrize("variant", VARIANTS)
+@pytest.mark.parametrize("geo", GEOS)
+def test_paged_single_shard(cuda, geo, variant):
+    g = GEOS[geo]
+    run_case(cuda, g, 1, 48, 5, 9 * g.page_tokens, VARIANTS[variant], seed=1)
+
+
+@pytest.mark.parametrize("variant", VARIANTS)
+@pytest.mark.parametrize("rule", [N.SHARD_MOD, N.SHARD_BLOCK])
+@pytest.mark.parametrize("n_shards", [2, 3, 8, 16])
+def test_paged_multi_shard_addressing(cuda, n_shards, rule, variant):
+    run_case(cuda, SMALL, n_shards, 11, 7, 6 * 16, VARIANTS[variant], rule=rule, seed=n_shards)
+
+
+@pytest.mark.parametrize("variant", VARIANTS)
+def test_every_tail_length(cuda, variant):
+    """One request per tail length 1..page_tokens (and exact multiples)."""
+    g = SMALL
+    for tail in range(1, g.page_tokens + 1):
+        run_case(cuda, g, 1, 8, 1, 16 + tail, VARIANTS[variant], seed=tail, min_tokens=16 + tail)
+        run_case(cuda, g, 1, 8, 1, tail, VARIANTS[variant], seed=tail, min_tokens=tail)
+
+
+@pytest.mark.parametrize("variant", VARIANTS)
+def test_many_small_requests_more_items_than_grid(cuda, variant):
+    run_case(cuda, B.GEO_A, 2, 2048, 64, 1024, VARIANTS[variant], seed=5, fill="normal", min_tokens=128)
+
+
+@pytest.mark.parametrize("seg", [1024, 4096, 16384, 65536])
+@pytest.mark.parametrize("variant", VARIANTS)
+def test_segment_sizes(cuda, native, variant, seg):
+    old = native.bikv_get_tuning(b"seg_bytes")
+    try:
+        assert native.bikv_set_tuning(b"seg_bytes", seg) == 0
+        run_case(cuda, GEOS["C-lite"], 1, 32, 3, 100, VARIANTS[variant], seed=seg)
+    finally:
+        native.bikv_set_tuning(b"seg_bytes", old)
+
+
+@pytest.mark.parametrize("stages", [2, 3, 8, 12])
+def test_bulk_stage_counts(cuda, native, stages):
+    old = native.bikv_get_tuning(b"bulk_stages")
+    try:
+        assert native.bikv_set_tuning(b"bulk_stages", stages) == 0
+        run_case(cuda, B.GEO_B, 1, 64, 4, 200, N.VARIANT_BULK, seed=stages)
+    finally:
+        native.bikv_set_tuning(b"bulk_stages", old)
+
+
+def test_packed_single_tensor_like_the_reference(cuda):
+    """All items of a combined task land back to back in ONE tensor (the reference's
+    running dest_offsets)."""
+    g = SMALL
+    pages = [[5, 9, 2], [7], [11, 3]]
+    tokens = [40, 16, 17]
+    plan = build_plan(pages, tokens, g.page_tokens)
+    recs = [tuple(r) for r in plan.table.tolist()]
+    assert recs == O.plan_records(pages, tokens, g.page_tokens)
+    shards_cpu = make_shards(g, 1, 16, 3)
+    pool = B.ShardedPool.single(shards_cpu[0].to(cuda), g)
+    out = make_workers(g, [73], cuda)
+    B.PageMover(cuda).gather(pool, plan, out[0])
+    ref = make_workers(g, [73])
+    O.gather(shards_cpu, g, recs, ref)
+    assert equal_bits(out[0], ref[0])
+
+
+def test_device_plan_entry_points(cuda):
+    """bikv_gather / bikv_scatter with the plan already resident on the device."""
+    g = B.GEO_A
+    rng = np.random.default_rng(3)
+    lists, tokens = random_plan(rng, g, 256, 6, 500)
+    plan = build_plan([l.tolist() for l in lists], tokens.astype(np.int32), g.page_tokens,
+                      item_request=np.arange(6, dtype=np.int32), n_requests=6)
+    recs = [tuple(r) for r in plan.table.tolist()]
+    shards_cpu = make_shards(g, 1, 256, 4)
+    shard = shards_cpu[0].to(cuda)
+    pool = B.ShardedPool.single(shard, g)
+    mover = B.PageMover(cuda)
+    out = make_workers(g, tokens, cuda)
+    d_recs, d_reqs = mover.upload(plan, g, out)
+    for variant in VARIANTS.values():
+        for t in out:
+            t.zero_()
+        mover.gather_dev(pool, d_recs, d_reqs, variant=variant)
+        ref = make_workers(g, tokens)
+        O.gather(shards_cpu, g, recs, ref)
+        for a, b in zip(out, ref):
+            assert equal_bits(a, b)
+        shard.zero_()
+        mover.scatter_dev(pool, d_recs, d_reqs, variant=variant)
+        torch.cuda.synchronize()
+        zero = [torch.zeros_like(shards_cpu[0])]
+        O.scatter(zero, g, recs, ref)
+        assert equal_bits(shard, zero[0])
+        shard.copy_(shards_cpu[0])
+
+
+def test_config0_round_trip(cuda):
+    """Config 0: gather every request, scatter into a zeroed pool, compare with the
+    oracle and with the original pool on the touched tokens."""
+    w = W.config0()
+    g = w.geom
+    pool_cpu = torch.randn(g.pool_shape(w.pages_per_shard), generator=torch.Generator().manual_seed(0)).to(g.dtype)
+    plan = w.plan()
+    recs = [tuple(r) for r in plan.table.tolist()]
+    mover = B.PageMover(cuda)
+    shard = pool_cpu.to(cuda)
+    out = make_workers(g, w.request_tokens, cuda)
+    mover.gather(B.ShardedPool.single(shard, g), plan, out)
+    ref = make_workers(g, w.request_tokens)
+    O.gather([pool_cpu], g, recs, ref)
+    for a, b in zip(out, ref):
+        assert equal_bits(a, b)
+    fresh = torch.zeros_like(shard)
+    mover.scatter(B.ShardedPool.single(fresh, g), plan, out)
+    fresh_ref = torch.zeros_like(pool_cpu)
+    O.scatter([fresh_ref], g, recs, ref)
+    assert equal_bits(fresh, fresh_ref)
+    # touched tokens equal the original pool
+    t = plan.table
+    full = t[t[:, 1] == g.page_tokens, 0]
+    assert equal_bits(fresh[full.tolist()], pool_cpu[full.tolist()])
+
+
+def test_invalid_plans_are_rejected_before_launch(cuda):
+    g = SMALL
+    shard = torch.zeros(g.pool_shape(8), dtype=g.dtype, device=cuda)
+    pool = B.ShardedPool.single(shard, g)
+    mover = B.PageMover(cuda)
+    out = make_workers(g, [32], cuda)
+    launches = N.lib().bikv_launch_count()
+    for table, status in [([[8, 16, 0, 0]], N.ERR_PAGE_RANGE), ([[0, 16, 0, 17]], N.ERR_DST_RANGE),
+                          ([[0, 17, 0, 0]], N.ERR_PLAN), ([[0, 16, 1, 0]], N.ERR_BAD_ARG)]:
+        with pytest.raises(B.BikvError) as e:
+            mover.gather(pool, Plan.from_table(np.array(table), 1), out)
+        assert e.value.status == status
+    with pytest.raises(B.BikvError) as e:
+        mover.scatter(pool, Plan.from_table(np.array([[1, 16, 0, 0], [1, 16, 0, 16]]), 1), out)
+    assert e.value.status == N.ERR_OVERLAP
+    assert N.lib().bikv_launch_count() == launches
+    assert int(shard.abs().sum()) == 0
+
+
+def test_full_size_config1_properties(cuda):
+    """Config 1 at full size (65,536-page pool, 64 requests): properties that need no
+    oracle pass over 10 GB -- (1) scatter(gather(pool)) into a zeroed pool and a second
+    gather reproduce the first gather bit for bit, (2) per-request checksums match
+    checksums computed directly from the pool pages, (3) untouched pages stay zero."""
+    free, _ = torch.cuda.mem_get_info()
+    w = W.config1()
+    g = w.geom
+    need = w.pages_per_shard * g.page_bytes + 2 * w.payload_bytes + (4 << 30)
+    if free < need:
+        pytest.skip(f"needs {need >> 30} GiB of device memory")
+    shard = torch.empty(g.pool_shape(w.pages_per_shard), dtype=g.dtype, device=cuda)
+    W.fill_normal_(shard, seed=1)
+    plan = w.plan()
+    mover = B.PageMover(cuda)
+    pool = B.ShardedPool.single(shard, g)
+    first = make_workers(g, w.request_tokens, cuda)
+    mover.gather(pool, plan, first)
+    # (2) checksum of each request against the pool pages read directly with torch
+    for r in (0, 17, 63):
+        ids = torch.from_numpy(w.page_lists[r].astype(np.int64)).to(cuda)
+        pages = shard[ids]                                  # [n, L, 2, P, H, D]
+        want = pages.permute(1, 2, 0, 3, 4, 5).reshape(g.n_layers, 2, -1, g.n_kv_heads, g.head_dim)
+        want = want[:, :, : int(w.request_tokens[r])]
+        assert torch.equal(first[r].view(torch.int16), want.contiguous().view(torch.int16))
+    # (1) round trip through a zeroed pool
+    touched = torch.from_numpy(np.concatenate(w.page_lists).astype(np.int64)).to(cuda)
+    shard.zero_()
+    mover.scatter(pool, plan, first)
+    second = make_workers(g, w.request_tokens, cuda)
+    mover.gather(pool, plan, second)
+    torch.cuda.synchronize()
+    for a, b in zip(first, second):
+        assert torch.equal(a.view(torch.int16), b.view(torch.int16))
+    # (3) pages outside the plan were not written
+    mask = torch.ones(w.pages_per_shard, dtype=torch.bool, device=cuda)
+    mask[touched] = False
+    untouched = mask.nonzero().flatten()[:: 97]
+    assert int(shard[untouched].view(torch.int16).ne(0).sum()) == 0
+    mover.check_status()

@@ -17,7 +17,7 @@ thread_local int tl_cuda_error = 0;
 std::atomic<long long> g_launches{0};
 
 // Tuning knobs (plain atomics: readers take a snapshot per call).
-std::atomic<long long> g_ldst_ctas_per_sm{8};
+std::atomic<long long> g_ldst_ctas_per_sm{16};
 std::atomic<long long> g_bulk_ctas_per_sm{3};
 std::atomic<long long> g_bulk_stages{4};
 std::atomic<long long> g_seg_bytes{16384};
@@ -208,7 +208,9 @@ int launch_paged(const bikv_pool_desc* pool, const bikv_geometry* g, const bikv_
   const long long smem = (long long)stages * seg;
   while (per_sm > 1 && per_sm * (smem + 1024) > 227 * 1024) --per_sm;
   unsigned grid = (unsigned)std::min<long long>(items, (long long)di.sm_count * per_sm);
-  if (smem > 48 * 1024)
+  // The kernel also holds a few static bytes (its mbarriers), so opt in well
+  // before the 48 KiB default limit.
+  if (smem > 40 * 1024)
     BIKV_CUDA(cudaFuncSetAttribute(k_paged_bulk, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   k_paged_bulk<<<grid, 32, (size_t)smem, st>>>(a, stages);
   return after_launch();

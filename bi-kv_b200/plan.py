@@ -66,8 +66,9 @@ class Plan:
         store.numpy()[: len(table)] = table
         nreq = int(n_requests if n_requests is not None else (table[:, 2].max() + 1 if len(table) else 1))
         req_tokens = np.zeros(nreq, dtype=np.int64)
-        if len(table):
-            np.maximum.at(req_tokens, table[:, 2], (table[:, 1] + table[:, 3]).astype(np.int64))
+        ok = (table[:, 2] >= 0) & (table[:, 2] < nreq)   # bad rows are the validator's business
+        if ok.any():
+            np.maximum.at(req_tokens, table[ok, 2], (table[ok, 1] + table[ok, 3]).astype(np.int64))
         return cls(store, len(table), req_tokens)
 
 

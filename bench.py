@@ -30,8 +30,8 @@ sys.path.insert(0, ROOT)
 METRIC = "kv_page_gather_scatter_throughput"
 UNIT = "GB/s"
 # DRAM bytes per payload byte of one launch, from the ncu capture summarised under
-# profiles/ (None until a capture exists).
-NCU_TRAFFIC_PER_PAYLOAD_BYTE = None
+# profiles/k_paged_ldst_config1.md (small case, scaled by payload).
+NCU_TRAFFIC_PER_PAYLOAD_BYTE = 1.966
 
 
 def parse_args():

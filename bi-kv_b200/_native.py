@@ -40,6 +40,8 @@ SHARD_BLOCK = 1
 VARIANT_AUTO = 0
 VARIANT_LDST = 1
 VARIANT_BULK = 2
+STATIC_MAX_PAGES = 32768
+STATIC_MAX_REQUESTS = 1024
 
 
 class Geometry(C.Structure):
@@ -110,6 +112,10 @@ SIGNATURES = {
         C.c_int,
         [C.POINTER(PoolDesc), C.POINTER(Geometry), _P, C.c_int64, _P, C.c_int32, _P, C.c_int64,
          C.c_int, C.c_int, _P, _P],
+    ),
+    "bikv_gather_h_static": (
+        C.c_int,
+        [C.POINTER(PoolDesc), C.POINTER(Geometry), _P, C.c_int64, _P, C.c_int32, C.c_int, C.c_int, _P, _P],
     ),
     "bikv_copy_pages_flat": (C.c_int, [_P, _P, _P, _P, C.c_int64, C.c_int64, C.c_int32, _P]),
     "bikv_copy_range": (C.c_int, [_P, _P, C.c_int64, _P]),

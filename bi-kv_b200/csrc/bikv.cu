@@ -553,3 +553,65 @@ int bikv_pool_close(void* ptr) {
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------
+// bikv_gather_h_static: the gather for callers that cannot allocate.
+//
+// The plan staging area is this file-scope device array instead of a buffer the
+// caller (or anyone) allocates.  In host code the name `g_static_plan` is only
+// a stand-in for the symbol, not a device address: the address a kernel or a
+// copy may use comes from cudaGetSymbolAddress, looked up once per device with
+// that device current and cached below.
+// ---------------------------------------------------------------------------
+static __device__ __align__(256) unsigned char g_static_plan[BIKV_STATIC_PLAN_BYTES];
+
+namespace {
+std::mutex g_static_mu;
+void* g_static_addr[64] = {nullptr};
+
+// Device address of g_static_plan on the current device (set-up on first use).
+int static_plan_address(unsigned char** out) {
+  int dev = 0;
+  BIKV_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return BIKV_ERR_BAD_ARG;
+  std::lock_guard<std::mutex> lk(g_static_mu);
+  if (!g_static_addr[dev]) {
+    void* ptr = nullptr;
+    cudaError_t e = cudaGetSymbolAddress((void**)&ptr, g_static_plan);
+    if (e != cudaSuccess) return cuda_fail(e);
+    if (!ptr) return BIKV_ERR_CUDA;
+    g_static_addr[dev] = ptr;
+  }
+  *out = (unsigned char*)g_static_addr[dev];
+  return BIKV_OK;
+}
+}  // namespace
+
+extern "C" int bikv_gather_h_static(const bikv_pool_desc* pool, const bikv_geometry* geom,
+                                    const bikv_page_rec* recs_host, int64_t n_pages,
+                                    const bikv_request_desc* requests_host, int32_t n_requests,
+                                    int validate, int variant, int32_t* status_dev, void* stream) {
+  if (n_pages < 0 || n_requests < 0) return BIKV_ERR_BAD_ARG;
+  if (n_pages > BIKV_STATIC_MAX_PAGES || n_requests > BIKV_STATIC_MAX_REQUESTS) return BIKV_ERR_TOO_LARGE;
+  if (n_pages == 0) return BIKV_OK;
+  if (!recs_host || !requests_host || n_requests == 0) return BIKV_ERR_BAD_ARG;
+  for (int32_t r = 0; r < n_requests; ++r)
+    if (!requests_host[r].base) return BIKV_ERR_BAD_ARG;
+  if (validate) {
+    int rc = bikv_plan_validate(recs_host, n_pages, requests_host, n_requests, pool, geom, 0);
+    if (rc) return rc;
+  }
+  unsigned char* scratch = nullptr;
+  int rc = static_plan_address(&scratch);
+  if (rc) return rc;
+  // Records at the front, request table behind the record area's full extent.
+  unsigned char* d_recs = scratch;
+  unsigned char* d_reqs = scratch + (size_t)BIKV_STATIC_MAX_PAGES * sizeof(bikv_page_rec);
+  cudaStream_t st = (cudaStream_t)stream;
+  BIKV_CUDA(cudaMemcpyAsync(d_recs, recs_host, (size_t)n_pages * sizeof(bikv_page_rec),
+                            cudaMemcpyHostToDevice, st));
+  BIKV_CUDA(cudaMemcpyAsync(d_reqs, requests_host, (size_t)n_requests * sizeof(bikv_request_desc),
+                            cudaMemcpyHostToDevice, st));
+  return run(pool, geom, (const bikv_page_rec*)d_recs, n_pages, (const bikv_request_desc*)d_reqs,
+             n_requests, 0, variant, status_dev, stream);
+}

@@ -203,6 +203,39 @@ int bikv_scatter_h(const bikv_pool_desc* pool, const bikv_geometry* geom,
                    int variant, int32_t* status_dev, void* stream);
 
 /*
+ * Gather for callers that must not allocate.  No counterpart in the reference.
+ *
+ * Same meaning as bikv_gather_h, but the caller brings no plan staging buffer:
+ * the plan is uploaded into a fixed array that is part of this library's device
+ * image (BIKV_STATIC_PLAN_BYTES, resident on every GPU that loads the library
+ * until the process exits).  The call makes no cudaMalloc/cudaFree and calls no
+ * allocating library routine, so it is usable from a process whose serving
+ * engine has already reserved all of HBM for its KV pool (a later cudaMalloc
+ * there fails or has to wait for memory to be given back), and from a handler on
+ * the transfer path, where the device-wide synchronisation hidden inside
+ * cudaMalloc/cudaFree would stall every other stream's copies.
+ *
+ * Limits: n_pages <= BIKV_STATIC_MAX_PAGES and n_requests <=
+ * BIKV_STATIC_MAX_REQUESTS; larger plans are refused with BIKV_ERR_TOO_LARGE
+ * before anything is copied or launched (split the plan, or use bikv_gather_h).
+ * The first call on a device looks up the array's device address (with that
+ * device current); make that first call outside any stream capture.
+ * Every call on a device shares the one array: it still holds the previous
+ * call's plan, nothing in it needs to start at zero (each call overwrites the
+ * part it uses), and two calls whose GPU work overlaps -- different streams, or
+ * different threads -- race on it.  Serialise them on one stream.
+ * The caller still passes every input and output: pool, worker tensors,
+ * status_dev (may be NULL for BIKV_VARIANT_LDST, as for bikv_gather_h).
+ */
+#define BIKV_STATIC_MAX_PAGES 32768
+#define BIKV_STATIC_MAX_REQUESTS 1024
+#define BIKV_STATIC_PLAN_BYTES (BIKV_STATIC_MAX_PAGES * 16 + BIKV_STATIC_MAX_REQUESTS * 16)
+int bikv_gather_h_static(const bikv_pool_desc* pool, const bikv_geometry* geom,
+                         const bikv_page_rec* recs_host, int64_t n_pages,
+                         const bikv_request_desc* requests_host, int32_t n_requests,
+                         int validate, int variant, int32_t* status_dev, void* stream);
+
+/*
  * Flat page copy with the reference kernel's exact semantics
  * (SharedMemory/CUDA_Shared/copy_kernel.cu:10-36): for every page i and element
  * e < page_elems, dst[dst_off[i] + e] = src[src_off[i] + e]; offsets are in

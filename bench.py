@@ -43,6 +43,14 @@ def parse_args():
     ap.add_argument("--variant", default="auto", choices=["auto", "ldst", "bulk"])
     ap.add_argument("--pool-pages", type=int, default=65536, help="pages per GPU")
     ap.add_argument("--requests", type=int, default=64)
+    ap.add_argument("--geometry", default="B", choices=["A", "B", "C", "R"],
+                    help="KV geometry (B = the benchmark's; others are side measurements)")
+    ap.add_argument("--layout", default="paged", choices=["paged", "token_major"],
+                    help="pool layout (token_major = the reference's pool; a side measurement)")
+    ap.add_argument("--pages-from", default="all", choices=["all", "remote", "local"],
+                    help="N > 1 only: draw pages from all shards (the benchmark), or only remote / only local ones")
+    ap.add_argument("--only", default="both", choices=["both", "gather", "scatter"],
+                    help="side measurement: time one direction only (all ranks then move data the same way)")
     ap.add_argument("--small", action="store_true", help="profiling-sized case (2,048-page pool, 8 requests)")
     ap.add_argument("--tune", action="append", default=[], metavar="KNOB=VALUE")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -189,10 +197,17 @@ def config_dict(args, w):
         else f"config2: config-1 geometry, pool striped page_id mod {args.gpus}, {args.gpus - 1}/{args.gpus} of pages remote"
     c = {"workload": name, "pool_pages_per_gpu": args.pool_pages, "requests_per_gpu": args.requests,
          "request_lengths": "lognormal(median 2048, sigma 0.8) clipped to [64, 8192]",
-         "step": "gather all requests + scatter them back",
+         "step": "gather all requests + scatter them back" + ("" if args.gpus == 1 else
+                                                                  "; ranks phase-aligned by a host barrier after each direction"),
          "l2": "inputs larger than L2 (payload per launch is ~10 GB against 126 MB of L2)"}
     if args.small:
         c["workload"] += " [SMALL profiling case]"
+    if args.only != "both":
+        c["workload"] += f" [SIDE MEASUREMENT: {args.only} only]"
+    if args.pages_from != "all":
+        c["workload"] += f" [SIDE MEASUREMENT: {args.pages_from} pages only]"
+    if args.geometry != "B" or args.layout != "paged":
+        c["workload"] += f" [SIDE MEASUREMENT: geometry {args.geometry}, {args.layout} pool]"
     if w is not None:
         c.update({"pages_per_step_per_gpu": 2 * w.n_pages, "payload_bytes_per_direction_per_gpu": w.payload_bytes,
                   "page_bytes": w.geom.page_bytes})
@@ -238,15 +253,19 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
         cpu_group = dist.new_group(backend="gloo")
 
-    geom = W.GEO_B
+    geom = {"A": W.GEO_A, "B": W.GEO_B, "C": W.GEO_C,
+            "R": B.KVGeometry(28, 2, 128, 16, torch.float16)}[args.geometry]
+    if args.layout == "token_major":
+        geom = geom.with_layout(N.POOL_TOKEN_MAJOR)
     shard = B.ShardedPool.allocate_shard(geom, args.pool_pages, dev)
     W.fill_normal_(shard, seed=1234 + rank)
     if multi:
         pool = B.ShardedPool.exchange(shard, geom, group=cpu_group)
-        w = W.config2(rank, world, seed=0, pages_per_shard=args.pool_pages, n_requests=args.requests)
+        w = W.config2(rank, world, seed=0, pages_per_shard=args.pool_pages, n_requests=args.requests, geom=geom,
+                      pages_from=args.pages_from)
     else:
         pool = B.ShardedPool.single(shard, geom)
-        w = W.config1(seed=0, n_pages=args.pool_pages, n_requests=args.requests)
+        w = W.config1(seed=0, n_pages=args.pool_pages, n_requests=args.requests, geom=geom)
     plan = w.plan()
     tensors = [torch.zeros(geom.worker_shape(int(t)), dtype=geom.dtype, device=dev) for t in w.request_tokens]
     mover = B.PageMover(dev, variant=variant)
@@ -257,9 +276,25 @@ def main():
         if multi:
             dist.barrier(group=cpu_group)
 
+    do_g, do_s = args.only in ("both", "gather"), args.only in ("both", "scatter")
+    n_dirs = int(do_g) + int(do_s)
+
+    def phase_end():
+        """N > 1: ranks move data the same way at the same time (all gather, then all
+        scatter), as the reference's batch-synchronous scheduler drives its workers.  A
+        host barrier between phases keeps them aligned; unaligned ranks load one NVLink
+        direction with reads AND writes while the other idles."""
+        if multi:
+            stream.synchronize()
+            barrier()
+
     def step_resident():
-        mover.gather_dev(pool, d_recs, d_reqs)
-        mover.scatter_dev(pool, d_recs, d_reqs)
+        if do_g:
+            mover.gather_dev(pool, d_recs, d_reqs)
+            phase_end()
+        if do_s:
+            mover.scatter_dev(pool, d_recs, d_reqs)
+            phase_end()
 
     flat_begin = w.flat()
     item_tokens = w.request_tokens.astype("int32")
@@ -267,8 +302,12 @@ def main():
 
     def step_e2e():
         p = build_plan(flat_begin, item_tokens, geom.page_tokens, item_request=item_req, n_requests=w.n_requests)
-        mover.gather(pool, p, tensors)
-        mover.scatter(pool, p, tensors)
+        if do_g:
+            mover.gather(pool, p, tensors)
+            phase_end()
+        if do_s:
+            mover.scatter(pool, p, tensors)
+            phase_end()
         mover.check_status()          # 16-byte device->host read, synchronises the step
 
     sampler = ClockSampler(local_rank) if rank == 0 else None
@@ -277,7 +316,7 @@ def main():
     torch.cuda.synchronize()
 
     # ---- timed region: K resident steps, CUDA events on the launching stream ----
-    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(args.steps)]
     launches0 = lib.bikv_launch_count()
     barrier()
     torch.cuda.synchronize()
@@ -288,10 +327,17 @@ def main():
     t_begin.record(stream)
     for k in range(args.steps):
         ev[k][0].record(stream)
-        mover.gather_dev(pool, d_recs, d_reqs)
+        if do_g:
+            mover.gather_dev(pool, d_recs, d_reqs)
         ev[k][1].record(stream)
-        mover.scatter_dev(pool, d_recs, d_reqs)
+        if do_g:
+            phase_end()
+        ev[k][3].record(stream)
+        if do_s:
+            mover.scatter_dev(pool, d_recs, d_reqs)
         ev[k][2].record(stream)
+        if do_s:
+            phase_end()
     t_end.record(stream)
     torch.cuda.synchronize()
     barrier()
@@ -300,7 +346,7 @@ def main():
     launches = lib.bikv_launch_count() - launches0
     elapsed_ms = t_begin.elapsed_time(t_end)
     gather_ms = [e[0].elapsed_time(e[1]) for e in ev]
-    scatter_ms = [e[1].elapsed_time(e[2]) for e in ev]
+    scatter_ms = [e[3].elapsed_time(e[2]) for e in ev]
     mover.check_status()
 
     # ---- end to end through the Python API, host-resident plan ----
@@ -339,11 +385,15 @@ def main():
     if rank == 0:
         peak, peak_kind = measured_peaks()
         secs = elapsed_ms / 1e3
-        value = 2 * total_payload * args.steps / secs / 1e9
-        launch_ms = statistics.mean(gather_ms + scatter_ms)
+        value = n_dirs * total_payload * args.steps / secs / 1e9
+        launch_ms = statistics.mean((gather_ms if do_g else []) + (scatter_ms if do_s else []))
         achieved = 2 * payload / (launch_ms / 1e3) / 1e9
-        kernel = {N.VARIANT_LDST: "k_paged_ldst", N.VARIANT_BULK: "k_paged_bulk"}[
-            variant if variant != N.VARIANT_AUTO else int(lib.bikv_get_tuning(b"auto_variant"))]
+        chosen = variant if variant != N.VARIANT_AUTO else int(lib.bikv_get_tuning(b"auto_variant"))
+        if chosen == N.VARIANT_AUTO:
+            chosen = N.VARIANT_BULK if multi else N.VARIANT_LDST
+        kernel = {N.VARIANT_LDST: "k_paged_ldst", N.VARIANT_BULK: "k_paged_bulk"}[chosen]
+        if args.layout == "token_major":
+            kernel = "k_token_major"
         roofline = {
             "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
             "traffic": None if NCU_TRAFFIC_PER_PAYLOAD_BYTE is None else NCU_TRAFFIC_PER_PAYLOAD_BYTE * payload,
@@ -363,11 +413,11 @@ def main():
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "u16", "data": "synthetic",
-            "config": config_dict(args, w), "pages_per_s": 2 * total_pages * args.steps / secs,
+            "config": config_dict(args, w), "pages_per_s": n_dirs * total_pages * args.steps / secs,
             "roofline": roofline, "gpu_launches": total_launches, "clocks": clocks,
         }
         if e2e:
-            line["e2e"] = {"value": 2 * total_payload * args.steps / e2e["seconds"] / 1e9, "unit": UNIT,
+            line["e2e"] = {"value": n_dirs * total_payload * args.steps / e2e["seconds"] / 1e9, "unit": UNIT,
                            "h2d_bytes_per_step": e2e["h2d_bytes_per_step"],
                            "d2h_bytes_per_step": e2e["d2h_bytes_per_step"],
                            "ms_per_step": e2e["seconds"] / args.steps * 1e3,

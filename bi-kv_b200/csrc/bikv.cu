@@ -21,7 +21,7 @@ std::atomic<long long> g_ldst_ctas_per_sm{16};
 std::atomic<long long> g_bulk_ctas_per_sm{3};
 std::atomic<long long> g_bulk_stages{4};
 std::atomic<long long> g_seg_bytes{16384};
-std::atomic<long long> g_auto_variant{BIKV_VARIANT_LDST};
+std::atomic<long long> g_auto_variant{0};  // 0 = choose by shard count
 
 int cuda_fail(cudaError_t e) {
   tl_cuda_error = (int)e;
@@ -169,7 +169,12 @@ int launch_paged(const bikv_pool_desc* pool, const bikv_geometry* g, const bikv_
   DeviceInfo di;
   int rc = device_info(&di);
   if (rc) return rc;
-  if (variant == BIKV_VARIANT_AUTO) variant = (int)g_auto_variant.load();
+  // AUTO: ld/st when every page is local (0.97-0.99 of HBM copy bandwidth there, the
+  // bulk ring 0.93); the bulk ring when shards are peer mappings (its larger requests
+  // load NVLink better: 652 vs 626 GB/s per GPU measured on 8 GPUs).
+  if (variant == BIKV_VARIANT_AUTO)
+    variant = g_auto_variant.load() ? (int)g_auto_variant.load()
+                                    : (pool->n_shards > 1 ? BIKV_VARIANT_BULK : BIKV_VARIANT_LDST);
   if (variant != BIKV_VARIANT_LDST && variant != BIKV_VARIANT_BULK) return BIKV_ERR_BAD_ARG;
   if (variant == BIKV_VARIANT_BULK && !status) return BIKV_ERR_BAD_ARG;
 
@@ -270,7 +275,7 @@ Knob* find_knob(const char* name) {
       {"bulk_ctas_per_sm", &g_bulk_ctas_per_sm, 1, 16},
       {"bulk_stages", &g_bulk_stages, 2, kMaxStages},
       {"seg_bytes", &g_seg_bytes, 1024, 64 * 1024},
-      {"auto_variant", &g_auto_variant, BIKV_VARIANT_LDST, BIKV_VARIANT_BULK},
+      {"auto_variant", &g_auto_variant, 0, BIKV_VARIANT_BULK},
   };
   if (!name) return nullptr;
   for (auto& k : knobs)

@@ -100,7 +100,7 @@ def config1(seed: int = 0, n_pages: int = 65536, n_requests: int = 64, geom: KVG
 
 
 def config2(rank: int, world: int, seed: int = 0, pages_per_shard: int = 65536, n_requests: int = 64,
-            geom: KVGeometry = GEO_B) -> Workload:
+            geom: KVGeometry = GEO_B, pages_from: str = "all") -> Workload:
     """``world`` GPUs, pool striped by ``page_id mod world``; this rank's 64 requests draw
     pages uniformly over all shards.  Ranks draw from disjoint slices of one global
     permutation, so concurrent scatters never share a page."""
@@ -109,6 +109,11 @@ def config2(rank: int, world: int, seed: int = 0, pages_per_shard: int = 65536, 
     perm = rng.permutation(total).astype(np.int32)
     share = total // world
     mine = perm[rank * share:(rank + 1) * share]
+    if pages_from == "remote":      # side measurement: only pages of other shards
+        mine = mine[mine % world != rank]
+    elif pages_from == "local":
+        mine = mine[mine % world == rank]
+    share = len(mine)
     rrng = np.random.default_rng([seed, rank])
     tokens = lognormal_lengths(rrng, n_requests, 2048, 0.8, 64, 8192)
     counts = (tokens + geom.page_tokens - 1) // geom.page_tokens

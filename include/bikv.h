@@ -64,7 +64,8 @@ enum bikv_shard_rule {
 
 /* Copy engine selection for the paged layout. */
 enum bikv_variant {
-  BIKV_VARIANT_AUTO = 0,
+  BIKV_VARIANT_AUTO = 0, /* ld/st for a single-shard pool, bulk ring for a sharded one
+                            (override with the "auto_variant" knob: 1 or 2; 0 = this rule) */
   BIKV_VARIANT_LDST = 1, /* warp per chunk, 16-byte ld/st                              */
   BIKV_VARIANT_BULK = 2  /* cp.async.bulk global->shared->global ring per CTA          */
 };

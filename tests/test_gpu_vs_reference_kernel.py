@@ -1,0 +1,55 @@
+"""Speed of the flat page copy against the reference's own kernel (compiled from the
+reference's source into oracle/_ref) on the reference's micro-benchmark shape: 200 pages
+of 50 tokens, 28 layers x 2 KV heads x head 128, fp16 (test_page_ipc.py:41-44).  The new
+kernel must not be slower; both rates are printed (run pytest with -s to see them)."""
+import importlib.util
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import bikv_b200 as B
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _time(fn, iters=10):
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(iters):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / iters
+
+
+@pytest.mark.parametrize("page_size,n_pages", [(50, 200), (16, 2048)])
+def test_flat_copy_not_slower_than_reference_kernel(cuda, page_size, n_pages):
+    path = os.path.join(ROOT, "oracle", "_ref", "bikv_ref_kernel.so")
+    if not os.path.exists(path):
+        pytest.skip("oracle/_ref/bikv_ref_kernel.so not built")
+    spec = importlib.util.spec_from_file_location("bikv_ref_kernel", path)
+    ref = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(ref)
+    g = B.GEO_R
+    elems = page_size * g.token_elems
+    pool_pages = 2 * n_pages
+    cache = torch.randn((pool_pages * page_size,) + g.token_shape, device=cuda, dtype=torch.float16)
+    rng = np.random.default_rng(0)
+    src = torch.from_numpy((rng.permutation(pool_pages)[:n_pages] * elems).astype(np.int64)).to(cuda)
+    dst = torch.from_numpy((rng.permutation(n_pages) * elems).astype(np.int64)).to(cuda)
+    out = torch.zeros(n_pages * elems, dtype=torch.float16, device=cuda)
+    mover = B.PageMover(cuda)
+    # the reference launcher ends with cudaDeviceSynchronize; ours is asynchronous
+    t_ref = _time(lambda: ref.ref_copy_pages(cache, src, dst, out, page_size, 128, 2, 28, 2))
+    t_new = _time(lambda: mover.copy_pages_flat(cache, out, src, dst, elems))
+    nbytes = n_pages * elems * 2
+    print(f"\n[flat copy {n_pages} pages x {page_size} tokens = {nbytes / 2**20:.1f} MiB] "
+          f"reference kernel {nbytes / t_ref / 1e6:.1f} GB/s ({t_ref:.3f} ms), "
+          f"bikv_copy_pages_flat {nbytes / t_new / 1e6:.1f} GB/s ({t_new:.3f} ms), x{t_ref / t_new:.2f}")
+    assert t_new <= t_ref * 1.05

@@ -104,12 +104,82 @@ int after_launch() {
   return BIKV_OK;
 }
 
+// Token-major pool with 2-byte elements and head_dim a multiple of 8.
+int launch_token_major16(const bikv_pool_desc* pool, const bikv_geometry* g, const bikv_page_rec* recs,
+                         long long n_pages, const bikv_request_desc* reqs, int to_pool, cudaStream_t st,
+                         const DeviceInfo& di) {
+  const unsigned H = g->n_kv_heads, D = g->head_dim, L = g->n_layers;
+  const unsigned G = D / 8;
+  const unsigned Lp = L | 1u;
+  // Largest slab (Gs groups of 8 d) that divides G and keeps the tile within the
+  // budget below, so that a few CTAs share an SM and cover each other's phases.
+  const long long per_group = 8ll * H * Lp * 4;
+  const long long budget = std::min<long long>(di.max_optin_smem, 100 * 1024);
+  unsigned Gs = 0;
+  for (unsigned cand = G; cand >= 1; --cand) {
+    if (G % cand) continue;
+    if (per_group * cand <= budget) {
+      Gs = cand;
+      break;
+    }
+  }
+  if (Gs == 0) {
+    Gs = 1;
+    if (per_group > di.max_optin_smem) return BIKV_ERR_TOO_LARGE;
+  }
+  const long long smem = per_group * Gs;
+  const long long items = n_pages * g->page_tokens * (long long)(G / Gs);
+  if (items > 0x7fffffffll) return BIKV_ERR_TOO_LARGE;
+  TokenMajor16Args a;
+  memset(&a, 0, sizeof(a));
+  a.recs = reinterpret_cast<const uint4*>(recs);
+  a.reqs = reqs;
+  a.pool = to_dev(pool);
+  a.n_items = (unsigned)items;
+  a.page_tokens = g->page_tokens;
+  a.slabs = G / Gs;
+  a.Gs = Gs;
+  a.H = H;
+  a.D = D;
+  a.L = L;
+  a.Lp = Lp;
+  a.token_bytes = (unsigned long long)D * H * L * 4ull;
+  a.to_pool = to_pool;
+  auto fd = [](unsigned d) {
+    FastDiv f;
+    f.d = d;
+    f.m = d == 1 ? 0u : (unsigned)((1ull << 32) / d + 1);
+    return f;
+  };
+  a.div_L = fd(L);
+  a.div_H = fd(H);
+  a.div_HG = fd(H * Gs);
+  a.div_Gs = fd(Gs);
+  a.div_slabs = fd(a.slabs);
+  a.div_ptok = fd((unsigned)g->page_tokens);
+  // FastDiv is exact while dividend * divisor < 2^32.
+  if ((unsigned long long)items * std::max<unsigned>(a.slabs, (unsigned)g->page_tokens) >= (1ull << 32) ||
+      (unsigned long long)(Gs * 8ull * H * L) * std::max(L, H * Gs) >= (1ull << 32))
+    return BIKV_ERR_TOO_LARGE;
+  const long long per_sm = std::max<long long>(1, std::min<long long>(8, (220 * 1024) / (smem + 1024)));
+  const unsigned grid = (unsigned)std::min<long long>(items, (long long)di.sm_count * per_sm);
+  if (grid == 0) return BIKV_OK;
+  if (smem > 40 * 1024)
+    BIKV_CUDA(cudaFuncSetAttribute(k_token_major16, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  BIKV_CUDA(cudaFuncSetAttribute(k_token_major16, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                 cudaSharedmemCarveoutMaxShared));
+  k_token_major16<<<grid, 256, (size_t)smem, st>>>(a);
+  return after_launch();
+}
+
 int launch_token_major(const bikv_pool_desc* pool, const bikv_geometry* g, const bikv_page_rec* recs,
                        long long n_pages, const bikv_request_desc* reqs, int to_pool,
                        cudaStream_t st) {
   DeviceInfo di;
   int rc = device_info(&di);
   if (rc) return rc;
+  if (g->elt_bytes == 2 && g->head_dim % 8 == 0)
+    return launch_token_major16(pool, g, recs, n_pages, reqs, to_pool, st, di);
   const unsigned V = 16 / g->elt_bytes;
   const unsigned C = 2u * g->n_layers;
   const unsigned H = g->n_kv_heads, D = g->head_dim;

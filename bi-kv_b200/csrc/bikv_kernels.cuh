@@ -416,4 +416,173 @@ __global__ void __launch_bounds__(256) k_token_major(const __grid_constant__ Tok
   }
 }
 
+
+// ---------------------------------------------------------------------------
+// Token-major pool, 2-byte elements (fp16 / bf16): the fast path.
+//
+// A (K,V) pair of one (d, h, layer) is one 32-bit word of the pool row, and the
+// row of a token is [d][h][layer] words.  A CTA moves a slab of Gs groups of 8
+// consecutive d (all heads, all layers) of one token.  In shared memory the slab
+// is kept as [j = d%8][h][g = d/8][layer] with an ODD layer pitch, so that
+//   * worker side: lane (h, g) reads/writes its 8 words (j = 0..7) at a stride of
+//     one pitch between lanes -- no bank conflicts -- and a warp's 16-byte
+//     vectors of K (and of V) form one contiguous run of the worker tensor;
+//   * pool side: the slab is one contiguous run, moved in 16-byte units.
+// ---------------------------------------------------------------------------
+// Division by a runtime constant as one multiply-high: exact while n * d < 2^32
+// (items, words and rows of a slab are far below that).
+struct FastDiv {
+  unsigned d, m;  // m = floor(2^32 / d) + 1, or 0 when d == 1
+  __device__ __forceinline__ unsigned div(unsigned n) const { return d == 1 ? n : __umulhi(n, m); }
+};
+
+struct TokenMajor16Args {
+  const uint4* recs;
+  const bikv_request_desc* reqs;
+  PoolDev pool;
+  unsigned n_items;      // n_pages * page_tokens * slabs
+  unsigned page_tokens;
+  unsigned slabs;        // G / Gs
+  unsigned Gs;           // d-groups (of 8) per slab
+  unsigned H, D, L;
+  unsigned Lp;           // odd pitch >= L, in words
+  FastDiv div_L, div_H, div_HG, div_Gs, div_slabs, div_ptok;
+  unsigned long long token_bytes;  // D*H*L*4
+  int to_pool;
+};
+
+// Shared-memory word index of (d_local, h, l): layout [j = d%8][h][g = d/8][l].
+__device__ __forceinline__ unsigned tm16_index(const TokenMajor16Args& a, unsigned d_local, unsigned h, unsigned l) {
+  return (((d_local & 7) * a.H + h) * a.Gs + (d_local >> 3)) * a.Lp + l;
+}
+
+__global__ void __launch_bounds__(256) k_token_major16(const __grid_constant__ TokenMajor16Args a) {
+  extern __shared__ __align__(16) unsigned tm16_tile[];
+  unsigned* tile = tm16_tile;
+  const unsigned HG = a.H * a.Gs;
+  const unsigned slab_words = a.Gs * 8 * a.H * a.L;
+  const unsigned slab_units = slab_words >> 2;
+  const unsigned n_out = a.L * HG;
+  const unsigned row_elems = a.H * a.D;
+  const unsigned j_pitch = a.H * a.Gs * a.Lp;   // words between j and j+1
+
+  for (unsigned w = blockIdx.x; w < a.n_items; w += gridDim.x) {
+    const unsigned t = a.div_slabs.div(w);
+    const unsigned slab = w - t * a.slabs;
+    const unsigned page = a.div_ptok.div(t);
+    const unsigned tok = t - page * a.page_tokens;
+    const uint4 r = __ldg(a.recs + page);
+    if (tok >= r.y) continue;  // uniform across the CTA
+    const unsigned id = r.x;
+    unsigned shard;
+    unsigned long long local;
+    if (a.pool.rule == BIKV_SHARD_MOD) {
+      shard = id % (unsigned)a.pool.n_shards;
+      local = id / (unsigned)a.pool.n_shards;
+    } else {
+      shard = (unsigned)(id / a.pool.pages_per_shard);
+      local = id % a.pool.pages_per_shard;
+    }
+    uint4* pool_p = reinterpret_cast<uint4*>(a.pool.base[shard] + (local * a.page_tokens + tok) * a.token_bytes +
+                                             (unsigned long long)slab * slab_words * 4ull);
+    const longlong2 rq = __ldg(reinterpret_cast<const longlong2*>(a.reqs + r.z));
+    unsigned short* work = reinterpret_cast<unsigned short*>(rq.x);
+    const unsigned long long T_req = (unsigned long long)rq.y;
+    // Element offset of (plane 0, this token, h = 0, first d of the slab); a plane is
+    // T_req * row_elems elements further.
+    unsigned short* work_tok = work + (unsigned long long)(r.w + tok) * row_elems + slab * a.Gs * 8;
+    const unsigned long long plane_elems = T_req * row_elems;
+
+    if (!a.to_pool) {
+      // pool -> shared (16-byte units of the contiguous slab)
+      for (unsigned i0 = threadIdx.x; i0 < slab_units; i0 += 4 * blockDim.x) {
+        uint4 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const unsigned i = i0 + u * blockDim.x;
+          if (i < slab_units) v[u] = ld_stream16(pool_p + i);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const unsigned i = i0 + u * blockDim.x;
+          if (i < slab_units) {
+            const unsigned wd = i << 2;
+            const unsigned row = a.div_L.div(wd);
+            unsigned l = wd - row * a.L;
+            unsigned d_local = a.div_H.div(row);
+            unsigned h = row - d_local * a.H;
+            const unsigned vals[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              tile[tm16_index(a, d_local, h, l)] = vals[k];
+              if (++l == a.L) {
+                l = 0;
+                if (++h == a.H) { h = 0; ++d_local; }
+              }
+            }
+          }
+        }
+      }
+      __syncthreads();
+      // shared -> worker: one K vector and one V vector per (layer, h, g)
+      for (unsigned o = threadIdx.x; o < n_out; o += blockDim.x) {
+        const unsigned l = a.div_HG.div(o);
+        const unsigned hg = o - l * HG;
+        const unsigned h = a.div_Gs.div(hg);
+        const unsigned g = hg - h * a.Gs;
+        const unsigned* src = tile + hg * a.Lp + l;    // (h*Gs + g)*Lp + l, j = 0
+        unsigned wv[8];
+#pragma unroll
+        for (unsigned j = 0; j < 8; ++j) wv[j] = src[j * j_pitch];
+        uint4 kv, vv;
+        kv.x = __byte_perm(wv[0], wv[1], 0x5410); vv.x = __byte_perm(wv[0], wv[1], 0x7632);
+        kv.y = __byte_perm(wv[2], wv[3], 0x5410); vv.y = __byte_perm(wv[2], wv[3], 0x7632);
+        kv.z = __byte_perm(wv[4], wv[5], 0x5410); vv.z = __byte_perm(wv[4], wv[5], 0x7632);
+        kv.w = __byte_perm(wv[6], wv[7], 0x5410); vv.w = __byte_perm(wv[6], wv[7], 0x7632);
+        unsigned short* kdst = work_tok + (2ull * l) * plane_elems + h * a.D + g * 8;
+        st_stream16(kdst, kv);
+        st_stream16(kdst + plane_elems, vv);
+      }
+      __syncthreads();
+    } else {
+      for (unsigned o = threadIdx.x; o < n_out; o += blockDim.x) {
+        const unsigned l = a.div_HG.div(o);
+        const unsigned hg = o - l * HG;
+        const unsigned h = a.div_Gs.div(hg);
+        const unsigned g = hg - h * a.Gs;
+        const unsigned short* ksrc = work_tok + (2ull * l) * plane_elems + h * a.D + g * 8;
+        const uint4 kv = ld_stream16(ksrc);
+        const uint4 vv = ld_stream16(ksrc + plane_elems);
+        const unsigned ks[4] = {kv.x, kv.y, kv.z, kv.w};
+        const unsigned vs[4] = {vv.x, vv.y, vv.z, vv.w};
+        unsigned* dst = tile + hg * a.Lp + l;
+#pragma unroll
+        for (unsigned q = 0; q < 4; ++q) {
+          dst[(2 * q) * j_pitch] = __byte_perm(ks[q], vs[q], 0x5410);
+          dst[(2 * q + 1) * j_pitch] = __byte_perm(ks[q], vs[q], 0x7632);
+        }
+      }
+      __syncthreads();
+      for (unsigned i = threadIdx.x; i < slab_units; i += blockDim.x) {
+        const unsigned wd = i << 2;
+        const unsigned row = a.div_L.div(wd);
+        unsigned l = wd - row * a.L;
+        unsigned d_local = a.div_H.div(row);
+        unsigned h = row - d_local * a.H;
+        unsigned vals[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          vals[k] = tile[tm16_index(a, d_local, h, l)];
+          if (++l == a.L) {
+            l = 0;
+            if (++h == a.H) { h = 0; ++d_local; }
+          }
+        }
+        st_stream16(pool_p + i, make_uint4(vals[0], vals[1], vals[2], vals[3]));
+      }
+      __syncthreads();
+    }
+  }
+}
+
 }  // namespace bikv

@@ -139,3 +139,45 @@ def test_ipc_mapped_shards_across_processes():
             p.kill()
             out, _ = p.communicate()
         assert p.returncode == 0 and "RANK_OK" in out, f"rank {r}:\n{out[-3000:]}"
+
+
+def test_nvlink_ceilings_report():
+    """Reference points for the NVLink fractions: one contiguous 4 GiB range moved by
+    bikv_copy_range between two GPUs, pulled (loads from the peer) and pushed (stores
+    to the peer), one direction at a time and both directions at once.  Prints GB/s per
+    direction (run pytest with -s); asserts only that peer traffic is in an NVLink range."""
+    _need_gpus(2)
+    import ctypes as C
+    import time
+
+    lib = N.lib()
+    n = 4 << 30
+    buf = {d: [torch.zeros(n, dtype=torch.uint8, device=f"cuda:{d}") for _ in range(2)] for d in (0, 1)}
+    N.check(lib.bikv_enable_peer(0, 1))
+    N.check(lib.bikv_enable_peer(1, 0))
+    streams = {d: torch.cuda.Stream(device=f"cuda:{d}") for d in (0, 1)}
+
+    def copy(dev, dst, src):
+        with torch.cuda.device(dev):
+            N.check(lib.bikv_copy_range(C.c_void_p(dst.data_ptr()), C.c_void_p(src.data_ptr()), n,
+                                        C.c_void_p(streams[dev].cuda_stream)))
+
+    def rate(fn, iters=4):
+        fn()
+        torch.cuda.synchronize(0), torch.cuda.synchronize(1)
+        t = time.perf_counter()
+        for _ in range(iters):
+            fn()
+        torch.cuda.synchronize(0), torch.cuda.synchronize(1)
+        return n * iters / (time.perf_counter() - t) / 1e9
+
+    results = {
+        "pull, one direction": rate(lambda: copy(0, buf[0][0], buf[1][0])),
+        "pull, both directions": rate(lambda: (copy(0, buf[0][0], buf[1][0]), copy(1, buf[1][1], buf[0][1]))),
+        "push, one direction": rate(lambda: copy(0, buf[1][0], buf[0][0])),
+        "push, both directions": rate(lambda: (copy(0, buf[1][0], buf[0][0]), copy(1, buf[0][1], buf[1][1]))),
+    }
+    print()
+    for k, v in results.items():
+        print(f"[nvlink ceiling] contiguous {k}: {v:.1f} GB/s per direction")
+    assert all(v > 100 for v in results.values())

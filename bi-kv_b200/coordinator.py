@@ -1,0 +1,160 @@
+"""Coordinator-driven prefix-reuse workload (benchmark configuration 4), host side.
+
+Plays the coordinator's part for the data path: every request names a user; the user's
+cached history prefix is looked up in a ``MultiPageManager`` (hit -> the pages are
+GATHERED into the request's KV tensor; miss -> pages are allocated, LRU items evicted if
+the pool is full, and the prefix is SCATTERED in), and the request's new tokens are always
+written back as a fresh item.  The decisions follow the live branch of the reference's
+coordinator loop (``DistributedStorage/CacheCoordinator.py:180-236``: CHECK -> hit/miss
+through the page manager, SEND filled with ``cache_worker`` + ``cache_pages_list``, RECV ->
+``load_item``) with the page managers of ``page_manager.py``.
+
+Within one batch every gather is issued before any scatter, and every item a batch
+touches is protected from eviction until the batch is planned (the reference has the
+protection counters, ``PageManager.py:91-103``, and leaves the calls commented out,
+``Worker/Worker.py:150,209-211``); together these guarantee that no page is read after it
+has been recycled and no page is written twice in a batch.
+"""
+from __future__ import annotations
+
+import random
+from dataclasses import dataclass, field
+from typing import Iterator, List, Optional, Tuple
+
+import numpy as np
+
+from . import _native as N
+from .page_manager import MultiPageManager
+from .plan import Plan, build_plan
+
+
+@dataclass
+class Request:
+    request_id: int
+    user: int
+    prefix_tokens: int
+    new_tokens: int
+    worker: int
+
+    @property
+    def tokens(self) -> int:
+        return self.prefix_tokens + self.new_tokens
+
+
+class PrefixReuseWorkload:
+    """Seeded request stream: users ~ Zipf(s) over ``n_users`` ranks (inverse CDF), one fixed
+    prefix length per user ~ lognormal(median, sigma) clipped, new tokens ~ U[lo, hi]."""
+
+    def __init__(self, seed: int = 0, n_users: int = 100_000, zipf_s: float = 1.1, prefix_median: int = 1024,
+                 prefix_sigma: float = 0.8, prefix_clip: Tuple[int, int] = (128, 8192),
+                 new_tokens: Tuple[int, int] = (32, 256), n_requests: int = 20_000, batch: int = 64,
+                 n_workers: int = 4):
+        rng = np.random.default_rng(seed)
+        weights = np.arange(1, n_users + 1, dtype=np.float64) ** (-zipf_s)
+        cdf = np.cumsum(weights)
+        cdf /= cdf[-1]
+        self.users = np.searchsorted(cdf, rng.random(n_requests)).astype(np.int64)
+        plen = rng.lognormal(np.log(prefix_median), prefix_sigma, size=n_users)
+        self.prefix_of_user = np.clip(np.rint(plen), *prefix_clip).astype(np.int64)
+        self.new = rng.integers(new_tokens[0], new_tokens[1] + 1, size=n_requests).astype(np.int64)
+        self.n_users, self.n_requests, self.batch, self.n_workers = n_users, n_requests, batch, n_workers
+
+    def batches(self) -> Iterator[List[Request]]:
+        for at in range(0, self.n_requests, self.batch):
+            yield [Request(i, int(self.users[i]), int(self.prefix_of_user[self.users[i]]), int(self.new[i]),
+                           i % self.n_workers)          # request_id % workers, Scheduler/LLMScheduler.py:296-297
+                   for i in range(at, min(at + self.batch, self.n_requests))]
+
+
+@dataclass
+class BatchPlan:
+    """What one worker executes for one batch: tensors of ``tokens[i]`` tokens per request,
+    a gather plan (hits' prefixes) and a scatter plan (misses' prefixes + all new tokens)."""
+    requests: List[Request]
+    gather: Plan
+    scatter: Plan
+    hit: List[bool]
+    evicted: int = 0
+
+    @property
+    def tokens(self) -> List[int]:
+        return [r.tokens for r in self.requests]
+
+
+class PrefixCacheCoordinator:
+    def __init__(self, n_shards: int, pages_per_shard: int, page_tokens: int, order: str = "reference",
+                 seed: int = 0):
+        self.n_shards, self.pages_per_shard, self.page_tokens = n_shards, pages_per_shard, page_tokens
+        self.pm = MultiPageManager(pages_per_shard * page_tokens, page_tokens, n_shards,
+                                   rng=random.Random(seed), order=order)
+        self.hits = self.misses = 0
+        self._next_new_item = 1 << 40      # ids of written-back new-token items, never user ids
+        self._stored_tokens = {}           # item id -> tokens it holds
+
+    @property
+    def hit_rate(self) -> float:
+        n = self.hits + self.misses
+        return self.hits / n if n else 0.0
+
+    def _protect(self, shard: int, item) -> None:
+        self.pm.page_managers[shard].set_protected(item)
+
+    def plan_batch(self, requests: List[Request]) -> BatchPlan:
+        """Plans one worker's share of a batch.  Records are in request order; request ``i``
+        of the list uses worker tensor ``i``."""
+        g_pages, g_tokens, g_req, g_shard = [], [], [], []
+        s_pages, s_tokens, s_req, s_shard, s_off = [], [], [], [], []
+        hit, touched = [], []
+        stored_now = set()     # users whose prefix is being stored by THIS batch
+        for i, r in enumerate(requests):
+            shard, pages = self.pm.access_item(r.user)
+            if r.user in stored_now:
+                # Missed earlier in this batch: the pages exist but are filled only by this
+                # batch's scatter, which runs after its gathers.  The request computes its
+                # prefix like the first one did; nothing to read, nothing more to store.
+                self.misses += 1
+                hit.append(False)
+            elif shard is not None and self._stored_tokens.get(r.user) == r.prefix_tokens:
+                self.hits += 1
+                hit.append(True)
+                g_pages.append(pages), g_tokens.append(r.prefix_tokens), g_req.append(i), g_shard.append(shard)
+            else:
+                self.misses += 1
+                hit.append(False)
+                shard, pages = self.pm.load_item(r.user, r.prefix_tokens)
+                self._stored_tokens[r.user] = r.prefix_tokens
+                stored_now.add(r.user)
+                s_pages.append(pages), s_tokens.append(r.prefix_tokens), s_req.append(i)
+                s_shard.append(shard), s_off.append(0)
+            self._protect(shard, r.user)
+            touched.append((shard, r.user))
+            item = self._next_new_item
+            self._next_new_item += 1
+            shard, pages = self.pm.load_item(item, r.new_tokens)
+            self._stored_tokens[item] = r.new_tokens
+            self._protect(shard, item)
+            touched.append((shard, item))
+            s_pages.append(pages), s_tokens.append(r.new_tokens), s_req.append(i)
+            s_shard.append(shard), s_off.append(r.prefix_tokens)
+        for shard, item in touched:
+            self.pm.page_managers[shard].remove_protected(item)
+        # forget bookkeeping of evicted items
+        live = set().union(*self.pm.cached_ids)
+        if len(self._stored_tokens) > 2 * len(live) + 1024:
+            self._stored_tokens = {k: v for k, v in self._stored_tokens.items() if k in live}
+        n = len(requests)
+        gather = build_plan(g_pages, g_tokens, self.page_tokens, item_request=g_req, n_requests=n,
+                            item_shard=g_shard, pages_per_shard=self.pages_per_shard)
+        scatter = build_plan(s_pages, s_tokens, self.page_tokens, item_request=s_req, n_requests=n,
+                             item_shard=s_shard, pages_per_shard=self.pages_per_shard)
+        # A request's new tokens sit behind its prefix in the worker tensor; on a miss both
+        # its items are scattered and build_plan's running offset already places them so.
+        # When the prefix is not scattered (a hit, or a repeat of a user this batch already
+        # stores) the request's only scattered item must start at prefix_tokens.
+        table = scatter.table
+        with_prefix = set(s_req[k] for k in range(len(s_req)) if s_off[k] == 0)
+        for i in range(n):
+            if i not in with_prefix:
+                rows = table[:, 2] == i
+                table[rows, 3] += requests[i].prefix_tokens
+        return BatchPlan(requests, gather, scatter, hit)

@@ -41,8 +41,13 @@ def parse_args():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--variant", default="auto", choices=["auto", "ldst", "bulk"])
-    ap.add_argument("--pool-pages", type=int, default=65536, help="pages per GPU")
-    ap.add_argument("--requests", type=int, default=64)
+    ap.add_argument("--pool-pages", type=int, default=None, help="pages per GPU (default 65536; config3: 8192)")
+    ap.add_argument("--requests", type=int, default=None, help="requests per GPU (default 64; config3: 16)")
+    ap.add_argument("--workload", default="auto", choices=["auto", "config3", "config4"],
+                    help="auto = configuration 1 (N = 1) or 2 (N > 1), the benchmark; config3 = long-context "
+                         "geometry, requests streamed; config4 = coordinator-driven prefix reuse, N/2 shard GPUs + "
+                         "N/2 worker GPUs (both are additional measurements)")
+    ap.add_argument("--c4-requests", type=int, default=20000)
     ap.add_argument("--geometry", default="B", choices=["A", "B", "C", "R"],
                     help="KV geometry (B = the benchmark's; others are side measurements)")
     ap.add_argument("--layout", default="paged", choices=["paged", "token_major"],
@@ -214,6 +219,230 @@ def config_dict(args, w):
     return c
 
 
+
+# --------------------------------------------------------------------------- additional workloads
+def _carve(arena, geom, tokens_list):
+    """Worker tensors [layer, kv, T, head, dim] laid one after another in a flat arena."""
+    import torch
+    out, at = [], 0
+    for t in tokens_list:
+        n = geom.token_elems * int(t)
+        out.append(arena[at:at + n].view(geom.worker_shape(int(t))))
+        at += (n + 127) // 128 * 128
+    if at > arena.numel():
+        raise RuntimeError("worker arena too small")
+    return out
+
+
+def run_config3(ctx):
+    """Configuration 3: long-context geometry (80 layers, 8 KV heads, head 128, fp16), requests of
+    16k-32k tokens, STREAMED one at a time through a reused worker buffer (one request is up to
+    10 GiB); pool striped page_id mod N.  A step = every request gathered and scattered back."""
+    import torch
+    import torch.distributed as dist
+
+    import bikv_b200 as B
+    from bikv_b200 import _native as N
+    from bikv_b200 import workloads as W
+
+    args, rank, world, dev, lib, multi = (ctx[k] for k in ("args", "rank", "world", "dev", "lib", "multi"))
+    geom = W.GEO_C
+    shard = B.ShardedPool.allocate_shard(geom, args.pool_pages, dev)
+    W.fill_normal_(shard, seed=99 + rank)
+    pool = B.ShardedPool.exchange(shard, geom, group=ctx["cpu_group"]) if multi else B.ShardedPool.single(shard, geom)
+    reqs = W.config3(rank, world, pages_per_shard=args.pool_pages, n_requests=args.requests)
+    arena = torch.zeros(geom.token_elems * max(w.total_tokens for w in reqs), dtype=geom.dtype, device=dev)
+    mover = B.PageMover(dev, variant=ctx["variant"])
+    staged = []
+    for w in reqs:
+        t = _carve(arena, geom, [w.total_tokens])
+        staged.append(mover.upload(w.plan(), geom, t))
+    stream = torch.cuda.current_stream(dev)
+
+    def phase_end():
+        if multi:
+            stream.synchronize()
+            dist.barrier(group=ctx["cpu_group"])
+
+    def step(events=None):
+        for i, (recs, rq) in enumerate(staged):
+            if events:
+                events[i][0].record(stream)
+            mover.gather_dev(pool, recs, rq)
+            if events:
+                events[i][1].record(stream)
+            phase_end()
+            if events:
+                events[i][2].record(stream)
+            mover.scatter_dev(pool, recs, rq)
+            if events:
+                events[i][3].record(stream)
+            phase_end()
+
+    sampler = ClockSampler(ctx["local_rank"]) if rank == 0 else None
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    if multi:
+        dist.barrier(group=ctx["cpu_group"])
+    ev = [[[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in staged] for _ in range(args.steps)]
+    launches0 = lib.bikv_launch_count()
+    if sampler:
+        sampler.mark_start()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record(stream)
+    for k in range(args.steps):
+        step(ev[k])
+    t1.record(stream)
+    torch.cuda.synchronize()
+    if sampler:
+        sampler.mark_end()
+    mover.check_status()
+    elapsed_ms = t0.elapsed_time(t1)
+    g_ms = sum(e[0].elapsed_time(e[1]) for st in ev for e in st) / args.steps
+    s_ms = sum(e[2].elapsed_time(e[3]) for st in ev for e in st) / args.steps
+    payload = float(sum(w.payload_bytes for w in reqs))
+    pages = float(sum(w.n_pages for w in reqs))
+    launches = float(lib.bikv_launch_count() - launches0)
+    remote = sum(w.remote_fraction(rank) * w.payload_bytes for w in reqs) / payload
+    if multi:
+        t = torch.tensor([elapsed_ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        tot = torch.tensor([payload, pages, launches], dtype=torch.float64, device=dev)
+        dist.all_reduce(tot, op=dist.ReduceOp.SUM)
+        elapsed_ms, (tp, tpages, tl) = float(t[0]), tot.tolist()
+    else:
+        tp, tpages, tl = payload, pages, launches
+    clocks = sampler.finish() if sampler else None
+    if rank == 0:
+        peak, peak_kind = measured_peaks()
+        secs = elapsed_ms / 1e3
+        line = {
+            "metric": METRIC, "value": 2 * tp * args.steps / secs / 1e9, "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": elapsed_ms / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u16", "data": "synthetic",
+            "config": {"workload": f"config3: Llama-3-70B-like KV (80 layers, 8 KV heads, head 128, fp16, 16-token pages), "
+                                   f"{args.requests} requests per GPU of U[16k,32k] tokens streamed one at a time, pool "
+                                   f"{args.pool_pages} pages per GPU striped page_id mod {world} [ADDITIONAL MEASUREMENT]",
+                       "payload_bytes_per_direction_per_gpu": payload, "page_bytes": geom.page_bytes,
+                       "l2": "inputs larger than L2 (each request is 5-10 GB)"},
+            "pages_per_s": 2 * tpages * args.steps / secs, "gpu_launches": int(tl), "clocks": clocks,
+            "roofline": {"bound": "hbm" if not multi else "nvlink", "unit": "GB/s", "gather_ms_per_step": g_ms,
+                         "scatter_ms_per_step": s_ms, "remote_fraction": remote,
+                         "hbm_achieved": 2 * payload / ((g_ms + s_ms) / 2 / 1e3) / 1e9, "hbm_peak": peak,
+                         "hbm_frac": 2 * payload / ((g_ms + s_ms) / 2 / 1e3) / 1e9 / peak, "peak_kind": f"of {peak_kind}",
+                         "nvlink_in_GBps_per_gpu": remote * payload / (g_ms / 1e3) / 1e9,
+                         "nvlink_out_GBps_per_gpu": remote * payload / (s_ms / 1e3) / 1e9},
+        }
+        print(json.dumps(line), flush=True)
+    if multi:
+        dist.barrier(group=ctx["cpu_group"])
+        pool.close()
+
+
+def run_config4(ctx):
+    """Configuration 4: N/2 KVCache-shard GPUs + N/2 worker GPUs, config-1 geometry.  100,000 users
+    ~ Zipf(1.1), cached prefixes lognormal(median 1024, sigma 0.8) in [128, 8192] (sigma is not given
+    by the configuration; 0.8 as in configuration 1), new tokens U[32,256] written back, LRU eviction by
+    the MultiPageManager, batches of 64.  Every page a worker touches is remote.  Reports pages/s
+    (wall clock, host planning included, and device time only) and the hit rate."""
+    import torch
+    import torch.distributed as dist
+
+    import bikv_b200 as B
+    from bikv_b200 import _native as N
+    from bikv_b200 import workloads as W
+    from bikv_b200.coordinator import PrefixCacheCoordinator, PrefixReuseWorkload
+
+    args, rank, world, dev, lib, multi = (ctx[k] for k in ("args", "rank", "world", "dev", "lib", "multi"))
+    if world < 2 or world % 2:
+        raise SystemExit("config4 needs an even number of GPUs >= 2 (half shards, half workers)")
+    n_shards = n_workers = world // 2
+    is_shard = rank < n_shards
+    geom = W.GEO_B
+    worker_ranks = list(range(n_shards, world))
+    wgroup = dist.new_group(ranks=worker_ranks, backend="gloo")
+    handles = [None] * world
+    shard = None
+    if is_shard:
+        shard = torch.zeros(geom.pool_shape(args.pool_pages), dtype=geom.dtype, device=dev)
+        mine = B.ShardedPool.export_handle(shard)
+    else:
+        mine = None
+    dist.all_gather_object(handles, mine, group=ctx["cpu_group"])
+    result = None
+    if not is_shard:
+        import ctypes as C
+        bases = []
+        for h in handles[:n_shards]:
+            out = C.c_void_p()
+            N.check(lib.bikv_pool_import(h[0], int(h[1]), C.byref(out)), "bikv_pool_import")
+            bases.append(int(out.value))
+        pool = B.ShardedPool(bases, args.pool_pages, geom, rule=N.SHARD_BLOCK, device=dev, imported=list(bases))
+        me = rank - n_shards
+        wl = PrefixReuseWorkload(seed=0, n_workers=n_workers, n_requests=args.c4_requests, batch=64)
+        co = PrefixCacheCoordinator(n_shards, args.pool_pages, geom.page_tokens, order="fast")
+        per_worker = (64 + n_workers - 1) // n_workers
+        arena = torch.zeros(geom.token_elems * (8192 + 256) * per_worker, dtype=geom.dtype, device=dev)
+        mover = B.PageMover(dev, variant=ctx["variant"])
+        stream = torch.cuda.current_stream(dev)
+        ev = []
+        pages = payload = 0
+        launches0 = lib.bikv_launch_count()
+        dist.barrier(group=wgroup)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for batch in wl.batches():
+            plans = [co.plan_batch([r for r in batch if r.worker == k]) for k in range(n_workers)]
+            bp = plans[me]
+            tensors = _carve(arena, geom, bp.tokens)
+            e = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+            e[0].record(stream)
+            mover.gather(pool, bp.gather, tensors)
+            e[1].record(stream)
+            stream.synchronize()
+            dist.barrier(group=wgroup)
+            e[2].record(stream)
+            mover.scatter(pool, bp.scatter, tensors)
+            e[3].record(stream)
+            stream.synchronize()
+            dist.barrier(group=wgroup)
+            ev.append(e)
+            pages += bp.gather.n_pages + bp.scatter.n_pages
+            payload += (int(bp.gather.table[:, 1].sum()) + int(bp.scatter.table[:, 1].sum())) * geom.bytes_per_token
+        torch.cuda.synchronize()
+        wall = time.perf_counter() - t0
+        mover.check_status()
+        dev_ms = sum(e[0].elapsed_time(e[1]) + e[2].elapsed_time(e[3]) for e in ev)
+        t = torch.tensor([wall, dev_ms], dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=wgroup)
+        tot = torch.tensor([float(pages), float(payload), float(lib.bikv_launch_count() - launches0)], dtype=torch.float64)
+        dist.all_reduce(tot, op=dist.ReduceOp.SUM, group=wgroup)
+        if me == 0:
+            wall, dev_ms = t.tolist()
+            result = {
+                "metric": "kv_pages_per_second", "value": tot[0].item() / wall, "unit": "pages/s", "n_gpus": world,
+                "steps": len(ev), "warmup": 0, "ms_per_step": wall / len(ev) * 1e3, "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "dtype": "u16", "data": "synthetic",
+                "config": {"workload": f"config4: {n_shards} shard GPUs + {n_workers} worker GPUs, config-1 geometry, "
+                                       f"{wl.n_users} users Zipf(1.1), {wl.n_requests} requests in batches of 64, LRU "
+                                       f"eviction [ADDITIONAL MEASUREMENT]", "pool_pages_per_shard": args.pool_pages},
+                "hit_rate": co.hit_rate, "GBps_wall": tot[1].item() / wall / 1e9,
+                "pages_per_s_device_only": tot[0].item() / (dev_ms / 1e3),
+                "GBps_device_only": tot[1].item() / (dev_ms / 1e3) / 1e9,
+                "nvlink_GBps_per_worker_device_only": tot[1].item() / n_workers / (dev_ms / 1e3) / 1e9,
+                "host_planning": "page managers with order='fast' (heap), replicated on every worker",
+                "gpu_launches": int(tot[2].item()),
+            }
+        pool.close()
+    # shard ranks wait here while the workers run
+    out = [None] * world
+    dist.all_gather_object(out, result, group=ctx["cpu_group"])
+    if rank == 0:
+        print(json.dumps(next(r for r in out if r is not None)), flush=True)
+    del shard
+
+
 # --------------------------------------------------------------------------- GPU arm
 def main():
     args = parse_args()
@@ -222,6 +451,10 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if args.small:
         args.pool_pages, args.requests = 2048, 8
+    if args.pool_pages is None:
+        args.pool_pages = 8192 if args.workload == "config3" else 65536
+    if args.requests is None:
+        args.requests = 16 if args.workload == "config3" else 64
     if args.impl == "reference":
         run_reference_arm(args, rank)
         return
@@ -252,6 +485,15 @@ def main():
     if multi:
         dist.init_process_group("nccl", device_id=dev)
         cpu_group = dist.new_group(backend="gloo")
+
+    if args.workload != "auto":
+        ctx = dict(args=args, rank=rank, world=world, dev=dev, lib=lib, variant=variant, multi=multi,
+                   cpu_group=cpu_group if multi else None, local_rank=local_rank)
+        (run_config3 if args.workload == "config3" else run_config4)(ctx)
+        if multi:
+            dist.barrier(group=cpu_group)
+            dist.destroy_process_group()
+        return
 
     geom = {"A": W.GEO_A, "B": W.GEO_B, "C": W.GEO_C,
             "R": B.KVGeometry(28, 2, 128, 16, torch.float16)}[args.geometry]

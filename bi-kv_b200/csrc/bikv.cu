@@ -458,10 +458,29 @@ int bikv_plan_validate(const bikv_page_rec* recs, int64_t n_pages, const bikv_re
       return BIKV_ERR_DST_RANGE;
   }
   if (check_overlap) {
-    std::vector<int32_t> ids((size_t)n_pages);
-    for (int64_t i = 0; i < n_pages; ++i) ids[(size_t)i] = recs[i].page_id;
-    std::sort(ids.begin(), ids.end());
-    if (std::adjacent_find(ids.begin(), ids.end()) != ids.end()) return BIKV_ERR_OVERLAP;
+    if (total_pages <= (int64_t)1 << 26) {
+      // One bit per pool page (8 MiB at most), kept per thread between calls and
+      // cleared again bit by bit, so the check is O(n_pages).
+      thread_local std::vector<uint64_t> seen;
+      const size_t words = (size_t)((total_pages + 63) / 64);
+      if (seen.size() < words) seen.assign(words, 0);
+      bool dup = false;
+      int64_t done = 0;
+      for (; done < n_pages && !dup; ++done) {
+        const uint32_t id = (uint32_t)recs[done].page_id;
+        uint64_t& wd = seen[id >> 6];
+        const uint64_t bit = 1ull << (id & 63);
+        dup = (wd & bit) != 0;
+        wd |= bit;
+      }
+      for (int64_t i = 0; i < done; ++i) seen[(uint32_t)recs[i].page_id >> 6] = 0;
+      if (dup) return BIKV_ERR_OVERLAP;
+    } else {
+      std::vector<int32_t> ids((size_t)n_pages);
+      for (int64_t i = 0; i < n_pages; ++i) ids[(size_t)i] = recs[i].page_id;
+      std::sort(ids.begin(), ids.end());
+      if (std::adjacent_find(ids.begin(), ids.end()) != ids.end()) return BIKV_ERR_OVERLAP;
+    }
   }
   return BIKV_OK;
 }

@@ -29,8 +29,10 @@ class PageMover:
         self.variant = variant
         self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
         self._scratch = torch.empty(1 << 20, dtype=torch.uint8, device=self.device)
-        self._req_cap = 0
-        self._req_host: Optional[torch.Tensor] = None
+        self._req_ring: list = []     # [pinned table, event of the upload that read it]
+        self._req_next = 0
+        self._req_slot = 0
+        self._inflight: list = []     # (event, plan): host buffers the GPU may not have read yet
 
     # -- helpers -----------------------------------------------------------
     def _stream(self, stream) -> int:
@@ -45,13 +47,22 @@ class PageMover:
 
     def request_table(self, geom: KVGeometry, tensors: Tensors) -> torch.Tensor:
         """Host (pinned) int64 [n, 2] table of (base pointer, tokens) for worker tensors
-        of shape ``geom.worker_shape(T)``."""
+        of shape ``geom.worker_shape(T)``.  Tables come from a small ring of pinned buffers;
+        a buffer is reused only after the upload that last read it has run."""
         ts = [tensors] if isinstance(tensors, torch.Tensor) else list(tensors)
         n = len(ts)
-        if self._req_host is None or self._req_cap < n:
-            self._req_cap = max(n, 64)
-            self._req_host = torch.empty((self._req_cap, 2), dtype=torch.int64).pin_memory()
-        tab = self._req_host.numpy()
+        slot = self._req_next % 8
+        self._req_next += 1
+        while len(self._req_ring) <= slot:
+            self._req_ring.append([None, None])
+        buf, ev = self._req_ring[slot]
+        if ev is not None and not ev.query():
+            ev.synchronize()
+        if buf is None or buf.shape[0] < n:
+            buf = torch.empty((max(n, 64), 2), dtype=torch.int64).pin_memory()
+        self._req_ring[slot] = [buf, None]
+        self._req_slot = slot
+        tab = buf.numpy()
         L, H, D = geom.n_layers, geom.n_kv_heads, geom.head_dim
         for i, t in enumerate(ts):
             if t.dim() != 5 or t.shape[0] != L or t.shape[1] != 2 or t.shape[3] != H or t.shape[4] != D:
@@ -62,7 +73,7 @@ class PageMover:
                 raise ValueError(f"worker tensor {i} lives on {t.device}, mover on {self.device}")
             tab[i, 0] = t.data_ptr()
             tab[i, 1] = t.shape[2]
-        return self._req_host[:n]
+        return buf[:n]
 
     # -- host-plan path ----------------------------------------------------
     def _run_h(self, fn, pool: ShardedPool, plan: Plan, tensors: Tensors, validate: bool,
@@ -79,6 +90,16 @@ class PageMover:
                 scratch.numel(), int(validate), self.variant if variant is None else variant,
                 C.c_void_p(self.status.data_ptr()), C.c_void_p(self._stream(stream)))
         N.check(rc, fn.__name__)
+        self._hold(plan, stream)
+
+    def _hold(self, plan: Plan, stream) -> None:
+        """Keeps ``plan`` (its pinned host buffer) alive until the stream has consumed the
+        upload, even if the caller drops it right after the call."""
+        self._inflight = [(e, p) for e, p in self._inflight if not e.query()]
+        ev = torch.cuda.Event()
+        ev.record(stream if stream is not None else torch.cuda.current_stream(self.device))
+        self._inflight.append((ev, plan))
+        self._req_ring[self._req_slot][1] = ev
 
     def gather(self, pool: ShardedPool, plan: Plan, tensors: Tensors, *, validate: bool = True,
                variant: Optional[int] = None, stream=None) -> None:

@@ -11,6 +11,7 @@ from __future__ import annotations
 
 import ctypes as C
 import itertools
+import threading
 from typing import Iterable, Optional, Sequence
 
 import numpy as np
@@ -22,11 +23,39 @@ REC_DTYPE = np.dtype([("page_id", "<i4"), ("valid_tokens", "<i4"), ("request", "
                       ("token_offset", "<i4")])
 
 
+class _PinnedRows:
+    """Recycles pinned int32 [rows, 4] buffers: pinning host memory costs far more than
+    building a plan, so buffers of dropped plans are handed out again.  A buffer comes
+    back only when its ``Plan`` is garbage-collected; ``PageMover`` keeps every plan it
+    has launched alive until the stream has passed the upload."""
+
+    def __init__(self):
+        self._free: list = []
+        self._lock = threading.Lock()
+
+    def get(self, n_rows: int) -> torch.Tensor:
+        n_rows = max(n_rows, 1)
+        with self._lock:
+            for i, t in enumerate(self._free):
+                if t.shape[0] >= n_rows:
+                    return self._free.pop(i)
+        cap = 1 << max(8, (n_rows - 1).bit_length())
+        t = torch.empty((cap, 4), dtype=torch.int32)
+        return t.pin_memory() if torch.cuda.is_available() else t
+
+    def put(self, t: torch.Tensor) -> None:
+        with self._lock:
+            if len(self._free) < 16:
+                self._free.append(t)
+                self._free.sort(key=lambda x: x.shape[0])
+
+
+_pinned = _PinnedRows()
+
+
 def _pinned_i32(n_rows: int, cols: int) -> torch.Tensor:
-    t = torch.empty((max(n_rows, 1), cols), dtype=torch.int32)
-    if torch.cuda.is_available():
-        t = t.pin_memory()
-    return t
+    assert cols == 4
+    return _pinned.get(n_rows)
 
 
 class Plan:
@@ -36,6 +65,14 @@ class Plan:
         self._store = recs                      # int32 [cap, 4], keeps the memory alive
         self.n_pages = int(n_pages)
         self.request_tokens = request_tokens    # int64 [n_requests]
+
+    def __del__(self):
+        store = self.__dict__.pop("_store", None)
+        if store is not None and _pinned is not None:
+            try:
+                _pinned.put(store)
+            except Exception:  # noqa: BLE001  (interpreter shutdown)
+                pass
 
     @property
     def n_requests(self) -> int:

@@ -306,9 +306,9 @@ def run_config3(ctx):
     launches = float(lib.bikv_launch_count() - launches0)
     remote = sum(w.remote_fraction(rank) * w.payload_bytes for w in reqs) / payload
     if multi:
-        t = torch.tensor([elapsed_ms], dtype=torch.float64, device=dev)
+        t = torch.tensor([elapsed_ms], dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        tot = torch.tensor([payload, pages, launches], dtype=torch.float64, device=dev)
+        tot = torch.tensor([payload, pages, launches], dtype=torch.float64)
         dist.all_reduce(tot, op=dist.ReduceOp.SUM)
         elapsed_ms, (tp, tpages, tl) = float(t[0]), tot.tolist()
     else:
@@ -362,6 +362,9 @@ def run_config4(ctx):
     geom = W.GEO_B
     worker_ranks = list(range(n_shards, world))
     wgroup = dist.new_group(ranks=worker_ranks, backend="gloo")
+    def note(msg):
+        print(f"[config4 rank {rank}] {msg}", file=sys.stderr, flush=True)
+
     handles = [None] * world
     shard = None
     if is_shard:
@@ -370,6 +373,7 @@ def run_config4(ctx):
     else:
         mine = None
     dist.all_gather_object(handles, mine, group=ctx["cpu_group"])
+    note("handles exchanged")
     result = None
     if not is_shard:
         import ctypes as C
@@ -391,6 +395,7 @@ def run_config4(ctx):
         launches0 = lib.bikv_launch_count()
         dist.barrier(group=wgroup)
         torch.cuda.synchronize()
+        note("pool mapped, arena ready, starting batches")
         t0 = time.perf_counter()
         for batch in wl.batches():
             plans = [co.plan_batch([r for r in batch if r.worker == k]) for k in range(n_workers)]
@@ -412,6 +417,7 @@ def run_config4(ctx):
             payload += (int(bp.gather.table[:, 1].sum()) + int(bp.scatter.table[:, 1].sum())) * geom.bytes_per_token
         torch.cuda.synchronize()
         wall = time.perf_counter() - t0
+        note(f"{len(ev)} batches done in {wall:.2f} s")
         mover.check_status()
         dev_ms = sum(e[0].elapsed_time(e[1]) + e[2].elapsed_time(e[3]) for e in ev)
         t = torch.tensor([wall, dev_ms], dtype=torch.float64)
@@ -436,6 +442,7 @@ def run_config4(ctx):
             }
         pool.close()
     # shard ranks wait here while the workers run
+    note("waiting for results")
     out = [None] * world
     dist.all_gather_object(out, result, group=ctx["cpu_group"])
     if rank == 0:
@@ -483,8 +490,12 @@ def main():
 
     multi = world > 1
     if multi:
-        dist.init_process_group("nccl", device_id=dev)
-        cpu_group = dist.new_group(backend="gloo")
+        # Host-side rendezvous only (handle exchange, barriers, max/sum of a few floats): the
+        # data path has no collective, so no NCCL communicator is created.  A rank that is
+        # gone makes the others fail after the timeout instead of waiting for ever.
+        import datetime
+        dist.init_process_group("gloo", timeout=datetime.timedelta(seconds=300))
+        cpu_group = dist.group.WORLD
 
     if args.workload != "auto":
         ctx = dict(args=args, rank=rank, world=world, dev=dev, lib=lib, variant=variant, multi=multi,
@@ -613,9 +624,9 @@ def main():
     payload = w.payload_bytes
     pages = w.n_pages
     if multi:
-        t = torch.tensor([elapsed_ms, e2e["seconds"] if e2e else 0.0], dtype=torch.float64, device=dev)
+        t = torch.tensor([elapsed_ms, e2e["seconds"] if e2e else 0.0], dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        tot = torch.tensor([float(payload), float(pages), float(launches)], dtype=torch.float64, device=dev)
+        tot = torch.tensor([float(payload), float(pages), float(launches)], dtype=torch.float64)
         dist.all_reduce(tot, op=dist.ReduceOp.SUM)
         elapsed_ms = float(t[0])
         if e2e:

@@ -48,6 +48,8 @@ def parse_args():
                          "geometry, requests streamed; config4 = coordinator-driven prefix reuse, N/2 shard GPUs + "
                          "N/2 worker GPUs (both are additional measurements)")
     ap.add_argument("--c4-requests", type=int, default=20000)
+    ap.add_argument("--c4-planner", default="native", choices=["native", "python"],
+                    help="config4: page directory in C++ (bikv_pm_*) or the Python page managers (order='fast')")
     ap.add_argument("--geometry", default="B", choices=["A", "B", "C", "R"],
                     help="KV geometry (B = the benchmark's; others are side measurements)")
     ap.add_argument("--layout", default="paged", choices=["paged", "token_major"],
@@ -352,7 +354,7 @@ def run_config4(ctx):
     import bikv_b200 as B
     from bikv_b200 import _native as N
     from bikv_b200 import workloads as W
-    from bikv_b200.coordinator import PrefixCacheCoordinator, PrefixReuseWorkload
+    from bikv_b200.coordinator import NativePrefixCacheCoordinator, PrefixCacheCoordinator, PrefixReuseWorkload
 
     args, rank, world, dev, lib, multi = (ctx[k] for k in ("args", "rank", "world", "dev", "lib", "multi"))
     if world < 2 or world % 2:
@@ -385,7 +387,8 @@ def run_config4(ctx):
         pool = B.ShardedPool(bases, args.pool_pages, geom, rule=N.SHARD_BLOCK, device=dev, imported=list(bases))
         me = rank - n_shards
         wl = PrefixReuseWorkload(seed=0, n_workers=n_workers, n_requests=args.c4_requests, batch=64)
-        co = PrefixCacheCoordinator(n_shards, args.pool_pages, geom.page_tokens, order="fast")
+        co = (NativePrefixCacheCoordinator(n_shards, args.pool_pages, geom.page_tokens) if args.c4_planner == "native"
+              else PrefixCacheCoordinator(n_shards, args.pool_pages, geom.page_tokens, order="fast"))
         per_worker = (64 + n_workers - 1) // n_workers
         arena = torch.zeros(geom.token_elems * (8192 + 256) * per_worker, dtype=geom.dtype, device=dev)
         mover = B.PageMover(dev, variant=ctx["variant"])
@@ -437,7 +440,8 @@ def run_config4(ctx):
                 "pages_per_s_device_only": tot[0].item() / (dev_ms / 1e3),
                 "GBps_device_only": tot[1].item() / (dev_ms / 1e3) / 1e9,
                 "nvlink_GBps_per_worker_device_only": tot[1].item() / n_workers / (dev_ms / 1e3) / 1e9,
-                "host_planning": "page managers with order='fast' (heap), replicated on every worker",
+                "host_planning": ("native page directory (bikv_pm_plan_prefix_batch)" if args.c4_planner == "native"
+                                  else "Python page managers with order='fast'") + ", replicated on every worker",
                 "gpu_launches": int(tot[2].item()),
             }
         pool.close()

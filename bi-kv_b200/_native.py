@@ -16,7 +16,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(_HERE, "csrc")
 INCLUDE = os.path.normpath(os.path.join(_HERE, "..", "include"))
 LIB_PATH = os.path.join(CSRC, "libbikv.so")
-SOURCES = ["bikv.cu"]
+SOURCES = ["bikv.cu", "bikv_pm.cpp"]
 HEADERS = ["bikv_kernels.cuh"]
 
 MAX_SHARDS = 16
@@ -124,7 +124,26 @@ SIGNATURES = {
     "bikv_pool_export": (C.c_int, [_P, C.c_char_p, C.POINTER(C.c_int64)]),
     "bikv_pool_import": (C.c_int, [C.c_char_p, C.c_int64, C.POINTER(_P)]),
     "bikv_pool_close": (C.c_int, [_P]),
+    # include/bikv_pm.h
+    "bikv_pm_create": (_P, [C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_uint64]),
+    "bikv_pm_destroy": (None, [_P]),
+    "bikv_pm_configure_tiers": (C.c_int, [_P, C.c_int64, C.c_int64]),
+    "bikv_pm_load_item": (C.c_int64, [_P, C.c_int64, C.c_int64, C.c_int32, C.c_int32, _P, _P, C.c_int64, _P, _P,
+                                      C.c_int64, _P]),
+    "bikv_pm_access_item": (C.c_int64, [_P, C.c_int64, _P, _P, C.c_int64]),
+    "bikv_pm_set_protected": (C.c_int, [_P, C.c_int64]),
+    "bikv_pm_remove_protected": (C.c_int, [_P, C.c_int64]),
+    "bikv_pm_advance_clock": (C.c_int, [_P, C.c_int64]),
+    "bikv_pm_free_pages": (C.c_int64, [_P, C.c_int32]),
+    "bikv_pm_item_count": (C.c_int64, [_P, C.c_int32]),
+    "bikv_pm_evictions": (C.c_int64, [_P]),
+    "bikv_pm_item_priority": (C.c_int, [_P, C.c_int64]),
+    "bikv_pm_plan_prefix_batch": (C.c_int, [_P, _P, _P, _P, C.c_int32, _P, _P, C.c_int64, _P, _P, C.c_int64, _P, _P]),
 }
+PM_LRU = 0
+PM_TIERED = 1
+PM_MISS = -100
+PM_FULL = -101
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -141,7 +160,9 @@ class BikvError(RuntimeError):
 
     def __init__(self, status: int, where: str = ""):
         self.status = int(status)
-        msg = lib().bikv_strerror(self.status).decode()
+        msg = {PM_MISS: "item not in the page directory",
+               PM_FULL: "page pool full: nothing left to evict"}.get(self.status) or \
+            lib().bikv_strerror(self.status).decode()
         if self.status == ERR_CUDA:
             msg += f" [cudaError {lib().bikv_last_cuda_error()}]"
         super().__init__(f"{where + ': ' if where else ''}{msg} ({self.status})")
@@ -151,7 +172,8 @@ def _stale() -> bool:
     if not os.path.exists(LIB_PATH):
         return True
     t = os.path.getmtime(LIB_PATH)
-    deps = [os.path.join(CSRC, f) for f in SOURCES + HEADERS] + [os.path.join(INCLUDE, "bikv.h")]
+    deps = [os.path.join(CSRC, f) for f in SOURCES + HEADERS] + [os.path.join(INCLUDE, h) for h in
+                                                                   ("bikv.h", "bikv_pm.h")]
     return any(os.path.getmtime(d) > t for d in deps if os.path.exists(d))
 
 

@@ -17,6 +17,7 @@ has been recycled and no page is written twice in a batch.
 """
 from __future__ import annotations
 
+import ctypes as C
 import random
 from dataclasses import dataclass, field
 from typing import Iterator, List, Optional, Tuple
@@ -83,10 +84,10 @@ class BatchPlan:
 
 class PrefixCacheCoordinator:
     def __init__(self, n_shards: int, pages_per_shard: int, page_tokens: int, order: str = "reference",
-                 seed: int = 0):
+                 seed: int = 0, rng=None):
         self.n_shards, self.pages_per_shard, self.page_tokens = n_shards, pages_per_shard, page_tokens
         self.pm = MultiPageManager(pages_per_shard * page_tokens, page_tokens, n_shards,
-                                   rng=random.Random(seed), order=order)
+                                   rng=rng if rng is not None else random.Random(seed), order=order)
         self.hits = self.misses = 0
         self._next_new_item = 1 << 40      # ids of written-back new-token items, never user ids
         self._stored_tokens = {}           # item id -> tokens it holds
@@ -158,3 +159,47 @@ class PrefixCacheCoordinator:
                 rows = table[:, 2] == i
                 table[rows, 3] += requests[i].prefix_tokens
         return BatchPlan(requests, gather, scatter, hit)
+
+
+class NativePrefixCacheCoordinator:
+    """Same planner on the native page directory: one ``bikv_pm_plan_prefix_batch`` call per
+    batch instead of a Python loop over requests (LRU policy, smallest-free-page allocation:
+    the decisions of ``PrefixCacheCoordinator(order="fast", rng=XorShiftChoice(seed))``)."""
+
+    def __init__(self, n_shards: int, pages_per_shard: int, page_tokens: int, seed: int = 0):
+        from .page_directory import PageDirectory
+
+        self.n_shards, self.pages_per_shard, self.page_tokens = n_shards, pages_per_shard, page_tokens
+        self.pm = PageDirectory(pages_per_shard * page_tokens, page_tokens, n_shards, policy="lru", seed=seed)
+        self.hits = self.misses = 0
+        self._next_item = C.c_int64(1 << 40)
+
+    @property
+    def hit_rate(self) -> float:
+        n = self.hits + self.misses
+        return self.hits / n if n else 0.0
+
+    def plan_batch(self, requests: List[Request]) -> BatchPlan:
+        from .plan import _pinned_i32
+
+        n = len(requests)
+        users = np.fromiter((r.user for r in requests), dtype=np.int64, count=n)
+        prefix = np.fromiter((r.prefix_tokens for r in requests), dtype=np.int32, count=n)
+        fresh = np.fromiter((r.new_tokens for r in requests), dtype=np.int32, count=n)
+        P = self.page_tokens
+        g_cap = int(((prefix + P - 1) // P).sum())
+        s_cap = g_cap + int(((fresh + P - 1) // P).sum())
+        g_store, s_store = _pinned_i32(g_cap, 4), _pinned_i32(s_cap, 4)
+        hit = np.zeros(max(n, 1), dtype=np.uint8)
+        n_g, n_s = C.c_int64(), C.c_int64()
+        ptr = lambda a: a.ctypes.data_as(C.c_void_p)
+        rc = N.lib().bikv_pm_plan_prefix_batch(self.pm.handle, ptr(users), ptr(prefix), ptr(fresh), n,
+                                               C.byref(self._next_item), C.c_void_p(g_store.data_ptr()), g_cap,
+                                               C.byref(n_g), C.c_void_p(s_store.data_ptr()), s_cap, C.byref(n_s),
+                                               ptr(hit))
+        N.check(rc, "bikv_pm_plan_prefix_batch")
+        hits = hit[:n].astype(bool).tolist()
+        self.hits += sum(hits)
+        self.misses += n - sum(hits)
+        tokens = np.array([r.tokens for r in requests], dtype=np.int64)
+        return BatchPlan(requests, Plan(g_store, n_g.value, tokens.copy()), Plan(s_store, n_s.value, tokens.copy()), hits)

@@ -13,9 +13,12 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 def declared_symbols():
-    text = open(os.path.join(ROOT, "include", "bikv.h")).read()
-    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    return sorted(set(re.findall(r"\b(bikv_[a-z_0-9]+)\s*\(", text)))
+    names = set()
+    for header in ("bikv.h", "bikv_pm.h"):
+        text = open(os.path.join(ROOT, "include", header)).read()
+        text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+        names |= set(re.findall(r"\b(bikv_[a-z_0-9]+)\s*\(", text))
+    return sorted(names)
 
 
 def test_header_and_binding_agree():

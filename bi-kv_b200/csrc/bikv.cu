@@ -104,6 +104,13 @@ int after_launch() {
   return BIKV_OK;
 }
 
+FastDiv fast_div(unsigned d) {
+  FastDiv f;
+  f.d = d;
+  f.m = d == 1 ? 0u : (unsigned)((1ull << 32) / d + 1);
+  return f;
+}
+
 // Token-major pool with 2-byte elements and head_dim a multiple of 8.
 int launch_token_major16(const bikv_pool_desc* pool, const bikv_geometry* g, const bikv_page_rec* recs,
                          long long n_pages, const bikv_request_desc* reqs, int to_pool, cudaStream_t st,
@@ -145,18 +152,12 @@ int launch_token_major16(const bikv_pool_desc* pool, const bikv_geometry* g, con
   a.Lp = Lp;
   a.token_bytes = (unsigned long long)D * H * L * 4ull;
   a.to_pool = to_pool;
-  auto fd = [](unsigned d) {
-    FastDiv f;
-    f.d = d;
-    f.m = d == 1 ? 0u : (unsigned)((1ull << 32) / d + 1);
-    return f;
-  };
-  a.div_L = fd(L);
-  a.div_H = fd(H);
-  a.div_HG = fd(H * Gs);
-  a.div_Gs = fd(Gs);
-  a.div_slabs = fd(a.slabs);
-  a.div_ptok = fd((unsigned)g->page_tokens);
+  a.div_L = fast_div(L);
+  a.div_H = fast_div(H);
+  a.div_HG = fast_div(H * Gs);
+  a.div_Gs = fast_div(Gs);
+  a.div_slabs = fast_div(a.slabs);
+  a.div_ptok = fast_div((unsigned)g->page_tokens);
   // FastDiv is exact while dividend * divisor < 2^32.
   if ((unsigned long long)items * std::max<unsigned>(a.slabs, (unsigned)g->page_tokens) >= (1ull << 32) ||
       (unsigned long long)(Gs * 8ull * H * L) * std::max(L, H * Gs) >= (1ull << 32))
@@ -172,12 +173,81 @@ int launch_token_major16(const bikv_pool_desc* pool, const bikv_geometry* g, con
   return after_launch();
 }
 
+
+// Token-major pool, 2-byte elements, head_dim % 8 == 0 and n_layers % 4 == 0.
+// Returns 1 if the geometry does not fit this kernel (caller falls back).
+int launch_token_major16v(const bikv_pool_desc* pool, const bikv_geometry* g, const bikv_page_rec* recs,
+                          long long n_pages, const bikv_request_desc* reqs, int to_pool, cudaStream_t st,
+                          const DeviceInfo& di) {
+  const unsigned H = g->n_kv_heads, D = g->head_dim, L = g->n_layers;
+  const unsigned G = D / 8, LU = L / 4;
+  unsigned ru_log2 = 3;
+  while ((1u << ru_log2) < LU) ++ru_log2;
+  const long long per_group = 8ll * H * (16ll << ru_log2);   // tile bytes per d-group
+  unsigned Gs = 0;
+  for (unsigned cand = G; cand >= 1; --cand) {
+    if (G % cand) continue;
+    if (per_group * cand <= 48 * 1024) {
+      Gs = cand;
+      break;
+    }
+  }
+  // Worker-side runs are Gs*16 bytes per head; below 128 bytes the older kernel, whose
+  // slab may hold more d-groups, does better (measured 0.61 against 0.22 of the HBM
+  // copy peak at 80 layers x 8 heads).
+  if (Gs < 8) return 1;
+  const long long tile = per_group * Gs;
+  const long long smem = to_pool ? tile : 2 * tile;
+  if (smem > di.max_optin_smem) return 1;
+  const long long items = n_pages * g->page_tokens * (long long)(G / Gs);
+  if (items > 0x7fffffffll) return BIKV_ERR_TOO_LARGE;
+  const unsigned long long rows = 8ull * Gs * H;
+  if ((unsigned long long)items * std::max<unsigned>(G / Gs, (unsigned)g->page_tokens) >= (1ull << 32) ||
+      rows * LU * std::max(std::max(LU, H), H * Gs) >= (1ull << 32))
+    return BIKV_ERR_TOO_LARGE;
+  TokenMajor16vArgs a;
+  memset(&a, 0, sizeof(a));
+  a.recs = reinterpret_cast<const uint4*>(recs);
+  a.reqs = reqs;
+  a.pool = to_dev(pool);
+  a.n_items = (unsigned)items;
+  a.page_tokens = g->page_tokens;
+  a.slabs = G / Gs;
+  a.Gs = Gs;
+  a.H = H;
+  a.D = D;
+  a.L = L;
+  a.LU = LU;
+  a.RU_log2 = ru_log2;
+  a.div_LU = fast_div(LU);
+  a.div_H = fast_div(H);
+  a.div_HG = fast_div(H * Gs);
+  a.div_Gs = fast_div(Gs);
+  a.div_slabs = fast_div(a.slabs);
+  a.div_ptok = fast_div((unsigned)g->page_tokens);
+  a.token_bytes = (unsigned long long)D * H * L * 4ull;
+  a.to_pool = to_pool;
+  const long long per_sm = std::max<long long>(1, std::min<long long>(6, (220 * 1024) / (smem + 1024)));
+  const unsigned grid = (unsigned)std::min<long long>(items, (long long)di.sm_count * per_sm);
+  if (grid == 0) return BIKV_OK;
+  BIKV_CUDA(cudaFuncSetAttribute(k_token_major16v, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)std::max<long long>(2 * tile, 48 * 1024)));
+  BIKV_CUDA(cudaFuncSetAttribute(k_token_major16v, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                 cudaSharedmemCarveoutMaxShared));
+  k_token_major16v<<<grid, 256, (size_t)smem, st>>>(a);
+  return after_launch();
+}
+
 int launch_token_major(const bikv_pool_desc* pool, const bikv_geometry* g, const bikv_page_rec* recs,
                        long long n_pages, const bikv_request_desc* reqs, int to_pool,
                        cudaStream_t st) {
   DeviceInfo di;
   int rc = device_info(&di);
   if (rc) return rc;
+  if (g->elt_bytes == 2 && g->head_dim % 8 == 0 && g->n_layers % 4 == 0) {
+    rc = launch_token_major16v(pool, g, recs, n_pages, reqs, to_pool, st, di);
+    if (rc != 1) return rc;
+  }
   if (g->elt_bytes == 2 && g->head_dim % 8 == 0)
     return launch_token_major16(pool, g, recs, n_pages, reqs, to_pool, st, di);
   const unsigned V = 16 / g->elt_bytes;

@@ -585,4 +585,195 @@ __global__ void __launch_bounds__(256) k_token_major16(const __grid_constant__ T
   }
 }
 
+
+// ---------------------------------------------------------------------------
+// Token-major pool, 2-byte elements, n_layers a multiple of 4: 16-byte shared
+// memory accesses on both sides.
+//
+// The slab (Gs groups of 8 d, all heads, all layers of one token) is kept in its
+// pool order, one row per (d, h) of L words, padded to RU 16-byte units (a power
+// of two >= 8).  The unit at position q of row (d, h) is stored at q ^ (hg & 7),
+// hg = h*Gs + d/8 the index of the row's (head, d-group).  Pool side: 16-byte units copied straight through
+// (cp.async on gather, so the next slab loads while this one is written out).
+// Worker side: thread (lq, h, g) reads the 8 rows j = 0..7 of its (h, g) at unit
+// lq -- the 8 lanes of a quarter warp have 8 consecutive hg, so the XOR sends them
+// to 8 different bank groups -- and turns the 8 x 4 (K,V) words into 4 K vectors and
+// 4 V vectors of 8 consecutive d, each part of a contiguous run of the warp.
+// ---------------------------------------------------------------------------
+struct TokenMajor16vArgs {
+  const uint4* recs;
+  const bikv_request_desc* reqs;
+  PoolDev pool;
+  unsigned n_items;      // n_pages * page_tokens * slabs
+  unsigned page_tokens;
+  unsigned slabs;        // G / Gs
+  unsigned Gs;           // d-groups (of 8) per slab
+  unsigned H, D, L;
+  unsigned LU;           // L / 4: 16-byte units per row
+  unsigned RU_log2;      // log2 of the padded row pitch in units
+  FastDiv div_LU, div_H, div_HG, div_Gs, div_slabs, div_ptok;
+  unsigned long long token_bytes;  // D*H*L*4
+  int to_pool;
+};
+
+struct TmItem {
+  uint4* pool_p;
+  unsigned short* work_tok;
+  unsigned long long plane_elems;
+  bool valid;
+};
+
+__device__ __forceinline__ TmItem tm16v_item(const TokenMajor16vArgs& a, unsigned w, unsigned slab_units) {
+  TmItem it;
+  it.valid = false;
+  if (w >= a.n_items) return it;
+  const unsigned t = a.div_slabs.div(w);
+  const unsigned slab = w - t * a.slabs;
+  const unsigned page = a.div_ptok.div(t);
+  const unsigned tok = t - page * a.page_tokens;
+  const uint4 r = __ldg(a.recs + page);
+  if (tok >= r.y) return it;
+  const unsigned id = r.x;
+  unsigned shard;
+  unsigned long long local;
+  if (a.pool.rule == BIKV_SHARD_MOD) {
+    shard = id % (unsigned)a.pool.n_shards;
+    local = id / (unsigned)a.pool.n_shards;
+  } else {
+    shard = (unsigned)(id / a.pool.pages_per_shard);
+    local = id % a.pool.pages_per_shard;
+  }
+  it.pool_p = reinterpret_cast<uint4*>(a.pool.base[shard] + (local * a.page_tokens + tok) * a.token_bytes) +
+              (unsigned long long)slab * slab_units;
+  const longlong2 rq = __ldg(reinterpret_cast<const longlong2*>(a.reqs + r.z));
+  const unsigned row_elems = a.H * a.D;
+  it.work_tok = reinterpret_cast<unsigned short*>(rq.x) + (unsigned long long)(r.w + tok) * row_elems +
+                slab * a.Gs * 8;
+  it.plane_elems = (unsigned long long)rq.y * row_elems;
+  it.valid = true;
+  return it;
+}
+
+// Shared-memory unit index of unit q of slab row `row` (= d_local*H + h).
+__device__ __forceinline__ unsigned tm16v_unit(const TokenMajor16vArgs& a, unsigned row, unsigned q) {
+  const unsigned d_local = a.div_H.div(row);
+  const unsigned h = row - d_local * a.H;
+  const unsigned hg = h * a.Gs + (d_local >> 3);
+  return (row << a.RU_log2) + (q ^ (hg & 7));
+}
+
+__device__ __forceinline__ void cp_async16(uint32_t dst_smem, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst_smem), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
+__global__ void __launch_bounds__(256) k_token_major16v(const __grid_constant__ TokenMajor16vArgs a) {
+  extern __shared__ __align__(16) uint4 tm16v_tile[];
+  const unsigned HG = a.H * a.Gs;
+  const unsigned rows = a.Gs * 8 * a.H;
+  const unsigned slab_units = rows * a.LU;
+  const unsigned tile_units = rows << a.RU_log2;
+  const unsigned n_out = a.LU * HG;
+
+  if (!a.to_pool) {
+    // Gather: two tiles; the slab of the next item streams in with cp.async while
+    // the current one is transposed out.
+    auto load = [&](const TmItem& it, uint4* tile) {
+      if (!it.valid) return;
+      const uint32_t base = smem_u32(tile);
+      for (unsigned i = threadIdx.x; i < slab_units; i += blockDim.x) {
+        const unsigned row = a.div_LU.div(i);
+        const unsigned q = i - row * a.LU;
+        cp_async16(base + tm16v_unit(a, row, q) * 16u, it.pool_p + i);
+      }
+    };
+    unsigned w = blockIdx.x;
+    TmItem cur = tm16v_item(a, w, slab_units);
+    unsigned buf = 0;
+    load(cur, tm16v_tile);
+    cp_async_commit();
+    while (w < a.n_items) {
+      const unsigned w_next = w + gridDim.x;
+      const TmItem nxt = tm16v_item(a, w_next, slab_units);
+      load(nxt, tm16v_tile + (buf ^ 1) * tile_units);
+      cp_async_commit();
+      // everything but the group just committed has landed
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+      __syncthreads();
+      if (cur.valid) {
+        const uint4* tile = tm16v_tile + buf * tile_units;
+        for (unsigned o = threadIdx.x; o < n_out; o += blockDim.x) {
+          const unsigned lq = a.div_HG.div(o);
+          const unsigned hg = o - lq * HG;
+          const unsigned h = a.div_Gs.div(hg);
+          const unsigned g = hg - h * a.Gs;
+          const unsigned q = lq ^ (hg & 7);
+          uint4 wv[8];
+#pragma unroll
+          for (unsigned j = 0; j < 8; ++j) wv[j] = tile[((((g << 3) + j) * a.H + h) << a.RU_log2) + q];
+          unsigned short* dst = cur.work_tok + (8ull * lq) * cur.plane_elems + h * a.D + g * 8;
+#pragma unroll
+          for (unsigned c = 0; c < 4; ++c) {
+            const unsigned x0 = (&wv[0].x)[c], x1 = (&wv[1].x)[c], x2 = (&wv[2].x)[c], x3 = (&wv[3].x)[c];
+            const unsigned x4 = (&wv[4].x)[c], x5 = (&wv[5].x)[c], x6 = (&wv[6].x)[c], x7 = (&wv[7].x)[c];
+            uint4 kv, vv;
+            kv.x = __byte_perm(x0, x1, 0x5410); vv.x = __byte_perm(x0, x1, 0x7632);
+            kv.y = __byte_perm(x2, x3, 0x5410); vv.y = __byte_perm(x2, x3, 0x7632);
+            kv.z = __byte_perm(x4, x5, 0x5410); vv.z = __byte_perm(x4, x5, 0x7632);
+            kv.w = __byte_perm(x6, x7, 0x5410); vv.w = __byte_perm(x6, x7, 0x7632);
+            st_stream16(dst + (2ull * c) * cur.plane_elems, kv);
+            st_stream16(dst + (2ull * c + 1) * cur.plane_elems, vv);
+          }
+        }
+      }
+      __syncthreads();  // the tile may be overwritten by the load after next
+      cur = nxt;
+      w = w_next;
+      buf ^= 1;
+    }
+    cp_async_wait_all();
+    return;
+  }
+
+  // Scatter: worker -> shared (transposing) -> pool (straight through).
+  for (unsigned w = blockIdx.x; w < a.n_items; w += gridDim.x) {
+    const TmItem it = tm16v_item(a, w, slab_units);
+    if (!it.valid) continue;  // uniform across the CTA
+    uint4* tile = tm16v_tile;
+    for (unsigned o = threadIdx.x; o < n_out; o += blockDim.x) {
+      const unsigned lq = a.div_HG.div(o);
+      const unsigned hg = o - lq * HG;
+      const unsigned h = a.div_Gs.div(hg);
+      const unsigned g = hg - h * a.Gs;
+      const unsigned q = lq ^ (hg & 7);
+      const unsigned short* src = it.work_tok + (8ull * lq) * it.plane_elems + h * a.D + g * 8;
+      uint4 kv[4], vv[4];
+#pragma unroll
+      for (unsigned c = 0; c < 4; ++c) {
+        kv[c] = ld_stream16(src + (2ull * c) * it.plane_elems);
+        vv[c] = ld_stream16(src + (2ull * c + 1) * it.plane_elems);
+      }
+#pragma unroll
+      for (unsigned j = 0; j < 8; ++j) {
+        // word c of row j: K_j of layer 4*lq + c in the low half, V_j in the high half
+        uint4 out;
+        const unsigned sel = (j & 1) ? 0x7632 : 0x5410;
+        out.x = __byte_perm((&kv[0].x)[j >> 1], (&vv[0].x)[j >> 1], sel);
+        out.y = __byte_perm((&kv[1].x)[j >> 1], (&vv[1].x)[j >> 1], sel);
+        out.z = __byte_perm((&kv[2].x)[j >> 1], (&vv[2].x)[j >> 1], sel);
+        out.w = __byte_perm((&kv[3].x)[j >> 1], (&vv[3].x)[j >> 1], sel);
+        tile[((((g << 3) + j) * a.H + h) << a.RU_log2) + q] = out;
+      }
+    }
+    __syncthreads();
+    for (unsigned i = threadIdx.x; i < slab_units; i += blockDim.x) {
+      const unsigned row = a.div_LU.div(i);
+      const unsigned q = i - row * a.LU;
+      st_stream16(it.pool_p + i, tile[tm16v_unit(a, row, q)]);
+    }
+    __syncthreads();
+  }
+}
+
 }  // namespace bikv

@@ -58,6 +58,8 @@ def parse_args():
                     help="N > 1 only: draw pages from all shards (the benchmark), or only remote / only local ones")
     ap.add_argument("--only", default="both", choices=["both", "gather", "scatter"],
                     help="side measurement: time one direction only (all ranks then move data the same way)")
+    ap.add_argument("--worker-layout", default="contiguous", choices=["contiguous", "nhd"],
+                    help="nhd = the worker's paged KV, one [slot, kv, head, dim] tensor per layer (side measurement)")
     ap.add_argument("--small", action="store_true", help="profiling-sized case (2,048-page pool, 8 requests)")
     ap.add_argument("--tune", action="append", default=[], metavar="KNOB=VALUE")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -211,6 +213,8 @@ def config_dict(args, w):
         c["workload"] += " [SMALL profiling case]"
     if args.only != "both":
         c["workload"] += f" [SIDE MEASUREMENT: {args.only} only]"
+    if args.worker_layout != "contiguous":
+        c["workload"] += " [SIDE MEASUREMENT: worker KV paged, one [slot, kv, head, dim] tensor per layer]"
     if args.pages_from != "all":
         c["workload"] += f" [SIDE MEASUREMENT: {args.pages_from} pages only]"
     if args.geometry != "B" or args.layout != "paged":
@@ -524,10 +528,31 @@ def main():
         pool = B.ShardedPool.single(shard, geom)
         w = W.config1(seed=0, n_pages=args.pool_pages, n_requests=args.requests, geom=geom)
     plan = w.plan()
-    tensors = [torch.zeros(geom.worker_shape(int(t)), dtype=geom.dtype, device=dev) for t in w.request_tokens]
     mover = B.PageMover(dev, variant=variant)
-    d_recs, d_reqs = mover.upload(plan, geom, tensors)
     stream = torch.cuda.current_stream(dev)
+    nhd = args.worker_layout == "nhd"
+    if nhd:
+        from bikv_b200.plan import build_block_plan
+        import numpy as _np
+        blocks = _np.random.default_rng(7).permutation(w.n_pages)
+        plan = build_block_plan(w.flat(), w.request_tokens.astype("int32"), geom.page_tokens, blocks)
+        layers = [torch.zeros((w.n_pages * geom.page_tokens, 2, geom.n_kv_heads, geom.head_dim), dtype=geom.dtype,
+                              device=dev) for _ in range(geom.n_layers)]
+
+        real_mover = mover
+
+        class _Nhd:   # same two calls as the contiguous path, on the paged worker KV
+            @staticmethod
+            def gather_dev(pool, *_):
+                real_mover.gather_nhd(pool, plan, layers, validate=False)
+
+            @staticmethod
+            def scatter_dev(pool, *_):
+                real_mover.scatter_nhd(pool, plan, layers, validate=False)
+        tensors, d_recs, d_reqs = [], None, None
+    else:
+        tensors = [torch.zeros(geom.worker_shape(int(t)), dtype=geom.dtype, device=dev) for t in w.request_tokens]
+        d_recs, d_reqs = mover.upload(plan, geom, tensors)
 
     def barrier():
         if multi:
@@ -535,6 +560,9 @@ def main():
 
     do_g, do_s = args.only in ("both", "gather"), args.only in ("both", "scatter")
     n_dirs = int(do_g) + int(do_s)
+    if nhd:
+        mover = _Nhd
+        args.no_e2e = True
 
     def phase_end():
         """N > 1: ranks move data the same way at the same time (all gather, then all
@@ -604,6 +632,8 @@ def main():
     elapsed_ms = t_begin.elapsed_time(t_end)
     gather_ms = [e[0].elapsed_time(e[1]) for e in ev]
     scatter_ms = [e[3].elapsed_time(e[2]) for e in ev]
+    if nhd:
+        mover = real_mover
     mover.check_status()
 
     # ---- end to end through the Python API, host-resident plan ----
@@ -651,6 +681,8 @@ def main():
         kernel = {N.VARIANT_LDST: "k_paged_ldst", N.VARIANT_BULK: "k_paged_bulk"}[chosen]
         if args.layout == "token_major":
             kernel = "k_token_major"
+        if nhd:
+            kernel = "k_paged_nhd"
         roofline = {
             "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
             "traffic": None if NCU_TRAFFIC_PER_PAYLOAD_BYTE is None else NCU_TRAFFIC_PER_PAYLOAD_BYTE * payload,

@@ -555,6 +555,66 @@ int bikv_plan_validate(const bikv_page_rec* recs, int64_t n_pages, const bikv_re
   return BIKV_OK;
 }
 
+static int run_nhd(const bikv_pool_desc* pool, const bikv_geometry* geom, const bikv_page_rec* recs_dev,
+                   int64_t n_pages, void* const* layer_bases_dev, int64_t slots_per_layer, int to_pool,
+                   void* stream) {
+  int rc = check_geometry(geom);
+  if (rc) return rc;
+  rc = check_pool(pool);
+  if (rc) return rc;
+  if (geom->pool_layout != BIKV_POOL_PAGED || n_pages < 0 || slots_per_layer < 0) return BIKV_ERR_BAD_ARG;
+  if (n_pages == 0) return BIKV_OK;
+  if (!recs_dev || !layer_bases_dev) return BIKV_ERR_BAD_ARG;
+  DeviceInfo di;
+  rc = device_info(&di);
+  if (rc) return rc;
+  NhdArgs a;
+  memset(&a, 0, sizeof(a));
+  a.recs = reinterpret_cast<const uint4*>(recs_dev);
+  a.layer_bases = reinterpret_cast<char* const*>(layer_bases_dev);
+  a.pool = to_dev(pool);
+  a.planes = 2u * geom->n_layers;
+  a.row_bytes = (unsigned)(geom->n_kv_heads * geom->head_dim * geom->elt_bytes);
+  a.row_vecs = a.row_bytes / 16;
+  a.row_vecs_m = a.row_vecs == 1 ? 0u : (unsigned)((1ull << 32) / a.row_vecs + 1);
+  a.plane_bytes = a.row_bytes * geom->page_tokens;
+  a.page_bytes = (unsigned long long)a.plane_bytes * a.planes;
+  const long long items = n_pages * (long long)a.planes;
+  if (items > 0x7fffffffll) return BIKV_ERR_TOO_LARGE;
+  a.n_items = (unsigned)items;
+  a.to_pool = to_pool;
+  const int threads = 256, warps = threads / 32;
+  const long long want = (items + warps - 1) / warps;
+  const unsigned grid = (unsigned)std::min<long long>(want, (long long)di.sm_count * g_ldst_ctas_per_sm.load());
+  k_paged_nhd<8><<<grid, threads, 0, (cudaStream_t)stream>>>(a);
+  return after_launch();
+}
+
+int bikv_gather_nhd(const bikv_pool_desc* pool, const bikv_geometry* geom, const bikv_page_rec* recs_dev,
+                    int64_t n_pages, void* const* layer_bases_dev, int64_t slots_per_layer, void* stream) {
+  return run_nhd(pool, geom, recs_dev, n_pages, layer_bases_dev, slots_per_layer, 0, stream);
+}
+
+int bikv_scatter_nhd(const bikv_pool_desc* pool, const bikv_geometry* geom, const bikv_page_rec* recs_dev,
+                     int64_t n_pages, void* const* layer_bases_dev, int64_t slots_per_layer, void* stream) {
+  return run_nhd(pool, geom, recs_dev, n_pages, layer_bases_dev, slots_per_layer, 1, stream);
+}
+
+int bikv_plan_validate_nhd(const bikv_page_rec* recs, int64_t n_pages, int64_t slots_per_layer,
+                           const bikv_pool_desc* pool, const bikv_geometry* geom, int check_overlap) {
+  if (slots_per_layer < 0) return BIKV_ERR_BAD_ARG;
+  // Same checks as for contiguous worker tensors, with one window of slots_per_layer
+  // tokens that every record must fall into.
+  if (n_pages > 0 && !recs) return BIKV_ERR_BAD_ARG;
+  for (int64_t i = 0; i < n_pages; ++i)
+    if (recs[i].token_offset < 0 || (int64_t)recs[i].token_offset + recs[i].valid_tokens > slots_per_layer)
+      return BIKV_ERR_DST_RANGE;
+  std::vector<bikv_page_rec> tmp(recs, recs + n_pages);
+  for (auto& r : tmp) r.request = 0;
+  bikv_request_desc window{nullptr, slots_per_layer};
+  return bikv_plan_validate(tmp.data(), n_pages, &window, 1, pool, geom, check_overlap);
+}
+
 int bikv_gather(const bikv_pool_desc* pool, const bikv_geometry* geom, const bikv_page_rec* recs_dev,
                 int64_t n_pages, const bikv_request_desc* requests_dev, int32_t n_requests,
                 int variant, int32_t* status_dev, void* stream) {

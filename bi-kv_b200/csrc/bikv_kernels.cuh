@@ -156,6 +156,79 @@ __global__ void __launch_bounds__(256) k_paged_ldst(const __grid_constant__ Page
 }
 
 // ---------------------------------------------------------------------------
+// Paged pool <-> paged worker KV ([slot][kv][head][dim] per layer).  One warp per
+// (page, plane): the plane of the page is one contiguous run of valid_tokens rows;
+// on the worker side row t lies 2 rows further than row t-1 (K and V rows of a
+// slot alternate).
+// ---------------------------------------------------------------------------
+struct NhdArgs {
+  const uint4* recs;
+  char* const* layer_bases;
+  PoolDev pool;
+  unsigned n_items;        // n_pages * planes
+  unsigned planes;
+  unsigned row_bytes;
+  unsigned row_vecs;       // row_bytes / 16
+  unsigned row_vecs_m;     // multiply-high constant for division by row_vecs (0 when 1)
+  unsigned plane_bytes;
+  unsigned long long page_bytes;
+  int to_pool;
+};
+
+template <int U>
+__global__ void __launch_bounds__(256) k_paged_nhd(const __grid_constant__ NhdArgs a) {
+  const unsigned lane = threadIdx.x & 31;
+  const unsigned warps_per_cta = blockDim.x >> 5;
+  const unsigned stride = gridDim.x * warps_per_cta;
+  for (unsigned w = blockIdx.x * warps_per_cta + (threadIdx.x >> 5); w < a.n_items; w += stride) {
+    const unsigned plane = w % a.planes;
+    const unsigned page = w / a.planes;
+    const uint4 r = __ldg(a.recs + page);
+    const unsigned id = r.x;
+    unsigned shard;
+    unsigned long long local;
+    if (a.pool.rule == BIKV_SHARD_MOD) {
+      shard = id % (unsigned)a.pool.n_shards;
+      local = id / (unsigned)a.pool.n_shards;
+    } else {
+      shard = (unsigned)(id / a.pool.pages_per_shard);
+      local = id % a.pool.pages_per_shard;
+    }
+    uint4* pool_p = reinterpret_cast<uint4*>(a.pool.base[shard] + local * a.page_bytes +
+                                             (unsigned long long)plane * a.plane_bytes);
+    const unsigned layer = plane >> 1, kv = plane & 1;
+    char* layer_base = reinterpret_cast<char*>(
+        __ldg(reinterpret_cast<const unsigned long long*>(a.layer_bases) + layer));
+    uint4* work_p = reinterpret_cast<uint4*>(layer_base + ((unsigned long long)r.w * 2 + kv) * a.row_bytes);
+    const unsigned n = r.y * a.row_vecs;
+    auto wi = [&](unsigned i) {   // worker-side vector index of pool-side vector i
+      const unsigned t = a.row_vecs_m ? __umulhi(i, a.row_vecs_m) : i;
+      return i + t * a.row_vecs;  // t*2*row_vecs + (i - t*row_vecs)
+    };
+    unsigned i = lane;
+    if (!a.to_pool) {
+      for (; i + 32u * (U - 1) < n; i += 32u * U) {
+        uint4 v[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) v[u] = ld_stream16(pool_p + i + 32 * u);
+#pragma unroll
+        for (int u = 0; u < U; ++u) st_stream16(work_p + wi(i + 32 * u), v[u]);
+      }
+      for (; i < n; i += 32) st_stream16(work_p + wi(i), ld_stream16(pool_p + i));
+    } else {
+      for (; i + 32u * (U - 1) < n; i += 32u * U) {
+        uint4 v[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) v[u] = ld_stream16(work_p + wi(i + 32 * u));
+#pragma unroll
+        for (int u = 0; u < U; ++u) st_stream16(pool_p + i + 32 * u, v[u]);
+      }
+      for (; i < n; i += 32) st_stream16(pool_p + i, ld_stream16(work_p + wi(i)));
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
 // Paged layout, bulk-async ring.  Thread 0 of each CTA runs a software
 // pipeline over `stages` shared-memory buffers of seg_bytes each:
 //   load(k+stages-1) in flight | wait full(k) | store(k) | refill stage of k-1

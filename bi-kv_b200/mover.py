@@ -33,6 +33,7 @@ class PageMover:
         self._req_next = 0
         self._req_slot = 0
         self._inflight: list = []     # (event, plan): host buffers the GPU may not have read yet
+        self._layer_tables: dict = {}
 
     # -- helpers -----------------------------------------------------------
     def _stream(self, stream) -> int:
@@ -99,7 +100,8 @@ class PageMover:
         ev = torch.cuda.Event()
         ev.record(stream if stream is not None else torch.cuda.current_stream(self.device))
         self._inflight.append((ev, plan))
-        self._req_ring[self._req_slot][1] = ev
+        if self._req_ring:
+            self._req_ring[self._req_slot][1] = ev
 
     def gather(self, pool: ShardedPool, plan: Plan, tensors: Tensors, *, validate: bool = True,
                variant: Optional[int] = None, stream=None) -> None:
@@ -132,6 +134,55 @@ class PageMover:
 
     def scatter_dev(self, pool, recs, reqs, *, variant=None, stream=None) -> None:
         self._run_d(N.lib().bikv_scatter, pool, recs, reqs, variant, stream)
+
+    # -- paged worker KV ("NHD": one [slot, kv, head, dim] tensor per layer) ----
+    def layer_table(self, geom: KVGeometry, layers: Sequence[torch.Tensor]) -> tuple:
+        """(device int64 [n_layers] of base pointers, slots per layer) for a worker's paged
+        KV cache; cached per set of tensors."""
+        key = tuple(t.data_ptr() for t in layers)
+        hit = self._layer_tables.get(key)
+        if hit is not None:
+            return hit
+        if len(layers) != geom.n_layers:
+            raise ValueError(f"{len(layers)} layer tensors for {geom.n_layers} layers")
+        slots = layers[0].shape[0]
+        for i, t in enumerate(layers):
+            if tuple(t.shape) != (slots, 2, geom.n_kv_heads, geom.head_dim) or not t.is_contiguous() \
+                    or t.element_size() != geom.elt_bytes or t.device != self.device:
+                raise ValueError(f"layer tensor {i}: want contiguous [{slots}, 2, {geom.n_kv_heads}, "
+                                 f"{geom.head_dim}] on {self.device}, got {tuple(t.shape)} on {t.device}")
+        table = torch.tensor(key, dtype=torch.int64).to(self.device)
+        if len(self._layer_tables) > 64:
+            self._layer_tables.clear()
+        self._layer_tables[key] = (table, slots, list(layers))
+        return self._layer_tables[key]
+
+    def _run_nhd(self, fn, pool: ShardedPool, plan: Plan, layers, validate: bool, check_overlap: bool, stream) -> None:
+        if plan.n_pages == 0:
+            return
+        table, slots, _ = self.layer_table(pool.geom, layers)
+        g = pool.geom.native()
+        if validate:
+            N.check(N.lib().bikv_plan_validate_nhd(C.c_void_p(plan.host_ptr), plan.n_pages, slots, C.byref(pool.desc),
+                                                   C.byref(g), int(check_overlap)), "bikv_plan_validate_nhd")
+        nbytes = plan.n_pages * 16
+        scratch = self._scratch_for(plan.n_pages, 0)
+        st = stream if stream is not None else torch.cuda.current_stream(self.device)
+        with torch.cuda.stream(st):
+            scratch[:nbytes].copy_(plan._store.view(torch.uint8).view(-1)[:nbytes], non_blocking=True)
+        N.check(fn(C.byref(pool.desc), C.byref(g), C.c_void_p(scratch.data_ptr()), plan.n_pages,
+                   C.c_void_p(table.data_ptr()), slots, C.c_void_p(int(st.cuda_stream))), fn.__name__)
+        self._hold(plan, stream)
+
+    def gather_nhd(self, pool: ShardedPool, plan: Plan, layers: Sequence[torch.Tensor], *, validate: bool = True,
+                   stream=None) -> None:
+        """Pool pages -> the worker's paged KV.  ``plan`` rows are (page_id, valid_tokens, -,
+        first slot); ``layers[l]`` is the layer-``l`` tensor ``[slots, 2, heads, dim]``."""
+        self._run_nhd(N.lib().bikv_gather_nhd, pool, plan, layers, validate, False, stream)
+
+    def scatter_nhd(self, pool: ShardedPool, plan: Plan, layers: Sequence[torch.Tensor], *, validate: bool = True,
+                    stream=None) -> None:
+        self._run_nhd(N.lib().bikv_scatter_nhd, pool, plan, layers, validate, True, stream)
 
     # -- flat copy ---------------------------------------------------------
     def copy_pages_flat(self, src: torch.Tensor, dst: torch.Tensor, src_off: torch.Tensor,

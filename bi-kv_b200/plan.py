@@ -168,3 +168,20 @@ def plan_from_combined_task(task, page_tokens: int, *, pages_per_shard: int = 0,
         tokens = [p.token_num for p in task.id_token_pair]
     shard = [cache_worker] * len(tokens) if block_sharded else None
     return build_plan(pages, tokens, page_tokens, item_shard=shard, pages_per_shard=pages_per_shard)
+
+
+def build_block_plan(cache_pages_list, item_tokens, page_tokens: int, block_ids, *, item_shard=None,
+                     pages_per_shard: int = 0) -> Plan:
+    """Plan for a worker whose KV is PAGED with blocks of ``page_tokens`` tokens: the k-th
+    page of the batch (items in order, pages in order) lands in worker block
+    ``block_ids[k]``, i.e. at slot ``block_ids[k] * page_tokens``.  Short last pages keep the
+    rule of :func:`build_plan`."""
+    plan = build_plan(cache_pages_list, item_tokens, page_tokens, item_shard=item_shard,
+                      pages_per_shard=pages_per_shard)
+    blocks = np.ascontiguousarray(block_ids, dtype=np.int64)
+    if len(blocks) != plan.n_pages:
+        raise ValueError(f"{plan.n_pages} pages but {len(blocks)} block ids")
+    if len(blocks) and (blocks.min() < 0 or blocks.max() * page_tokens > 0x7fffffff - page_tokens):
+        raise ValueError("block id out of range")
+    plan.table[:, 3] = (blocks * page_tokens).astype(np.int32)
+    return plan

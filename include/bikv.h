@@ -204,6 +204,30 @@ int bikv_scatter_h(const bikv_pool_desc* pool, const bikv_geometry* geom,
                    int variant, int32_t* status_dev, void* stream);
 
 /*
+ * Gather / scatter against a worker's PAGED KV instead of contiguous per-request
+ * tensors: one tensor per layer, laid out [slot][kv][head][dim] with slot =
+ * block * block_tokens + token -- the Worker's local_kvcache (Worker/Worker.py:68-78)
+ * that the model's paged prefill reads (Model/qwen2.py:169-181,273-276).  Nothing in
+ * the reference fills that cache from the pool; these entry points do it without an
+ * intermediate tensor.  For record i, token t < valid_tokens of pool page page_id maps
+ * to slot token_offset + t of every layer (rec.request is ignored).
+ *   layer_bases_dev  device array of n_layers pointers (one tensor per layer)
+ *   slots_per_layer  slots in each layer tensor (bounds for bikv_plan_validate_nhd)
+ * BIKV_POOL_PAGED pools only (BIKV_ERR_BAD_ARG otherwise).
+ */
+int bikv_gather_nhd(const bikv_pool_desc* pool, const bikv_geometry* geom,
+                    const bikv_page_rec* recs_dev, int64_t n_pages,
+                    void* const* layer_bases_dev, int64_t slots_per_layer, void* stream);
+int bikv_scatter_nhd(const bikv_pool_desc* pool, const bikv_geometry* geom,
+                     const bikv_page_rec* recs_dev, int64_t n_pages,
+                     void* const* layer_bases_dev, int64_t slots_per_layer, void* stream);
+/* Host-side check of a paged-worker plan: page ids in the pool, valid_tokens in
+ * 1..page_tokens, slots inside [0, slots_per_layer), and (check_overlap) no pool
+ * page named twice. */
+int bikv_plan_validate_nhd(const bikv_page_rec* recs, int64_t n_pages, int64_t slots_per_layer,
+                           const bikv_pool_desc* pool, const bikv_geometry* geom, int check_overlap);
+
+/*
  * Gather for callers that must not allocate.  No counterpart in the reference.
  *
  * Same meaning as bikv_gather_h, but the caller brings no plan staging buffer:

@@ -113,6 +113,24 @@ def scatter(shards: Sequence[torch.Tensor], geom, recs: Sequence[Rec], workers: 
 
 
 # --------------------------------------------------------------------------
+# Paged worker KV: one [slot, kv, head, dim] tensor per layer (Worker.py:68-78).
+# Record (page, valid, -, slot): token t of the page <-> slot + t of every layer.
+# --------------------------------------------------------------------------
+def gather_nhd(shards, geom, recs, layers, rule: int = SHARD_MOD) -> None:
+    for page_id, valid, _, slot in recs:
+        page = _page_view(shards, geom, int(page_id), rule)            # [L, 2, P, H, D]
+        for l in range(geom.n_layers):
+            layers[l][slot:slot + valid] = page[l, :, :valid].permute(1, 0, 2, 3)
+
+
+def scatter_nhd(shards, geom, recs, layers, rule: int = SHARD_MOD) -> None:
+    for page_id, valid, _, slot in recs:
+        page = _page_view(shards, geom, int(page_id), rule)
+        for l in range(geom.n_layers):
+            page[l, :, :valid] = layers[l][slot:slot + valid].permute(1, 0, 2, 3)
+
+
+# --------------------------------------------------------------------------
 # Flat page copy: copy_kernel.cu:10-36 verbatim in meaning (element offsets,
 # whole pages, pages applied in index order).
 # --------------------------------------------------------------------------

@@ -1,0 +1,118 @@
+"""Gather/scatter against the worker's paged KV (one [slot, kv, head, dim] tensor per
+layer), and a pool shard living in pinned host memory, against the oracle."""
+import numpy as np
+import pytest
+import torch
+
+import bikv_b200 as B
+from bikv_b200 import _native as N
+from bikv_b200.geometry import KVGeometry
+from bikv_b200.plan import Plan, build_block_plan, build_plan
+from oracle import bikv_oracle as O
+
+from helpers import equal_bits, make_shards, make_workers, normal, random_plan
+
+pytestmark = pytest.mark.gpu
+
+GEOS = {"small": KVGeometry(3, 2, 64, 16, torch.bfloat16), "B": B.GEO_B,
+        "row16": KVGeometry(2, 1, 8, 4, torch.float16), "A": B.GEO_A}
+
+
+@pytest.mark.parametrize("geo", GEOS)
+@pytest.mark.parametrize("n_shards", [1, 3])
+def test_paged_worker_kv(cuda, geo, n_shards):
+    g = GEOS[geo]
+    rng = np.random.default_rng(len(geo) + n_shards)
+    per, n_blocks = 20, 40
+    lists, tokens = random_plan(rng, g, n_shards * per, 4, 6 * g.page_tokens)
+    n_pages = sum(len(l) for l in lists)
+    blocks = rng.permutation(n_blocks)[:n_pages]
+    plan = build_block_plan([l.tolist() for l in lists], tokens.astype(np.int32), g.page_tokens, blocks)
+    recs = [tuple(r) for r in plan.table.tolist()]
+    assert [r[3] for r in recs] == (blocks * g.page_tokens).tolist()
+    shards_cpu = make_shards(g, n_shards, per, 5, fill="bits")
+    shards_gpu = [s.to(cuda) for s in shards_cpu]
+    pool = B.ShardedPool.from_tensors(shards_gpu, g)
+    mover = B.PageMover(cuda)
+    slots = n_blocks * g.page_tokens
+    layers_cpu = [normal((slots, 2, g.n_kv_heads, g.head_dim), g.dtype, 100 + l) for l in range(g.n_layers)]
+    layers_gpu = [t.to(cuda) for t in layers_cpu]
+    mover.gather_nhd(pool, plan, layers_gpu)
+    O.gather_nhd(shards_cpu, g, recs, layers_cpu)
+    torch.cuda.synchronize()
+    for a, b in zip(layers_gpu, layers_cpu):
+        assert equal_bits(a, b)                      # untouched slots keep their contents
+    fresh_cpu = [normal(t.shape, g.dtype, 300 + l) for l, t in enumerate(layers_cpu)]
+    mover.scatter_nhd(pool, plan, [t.to(cuda) for t in fresh_cpu])
+    O.scatter_nhd(shards_cpu, g, recs, fresh_cpu)
+    torch.cuda.synchronize()
+    for a, b in zip(shards_gpu, shards_cpu):
+        assert equal_bits(a, b)
+
+
+def test_paged_worker_kv_equals_contiguous_gather_reshaped(cuda):
+    """Same pages gathered contiguously and into blocks 0..n-1 hold the same tokens."""
+    g = B.GEO_A
+    pages = [7, 3, 12, 5]
+    plan_c = build_plan([pages], [64], 16)
+    plan_b = build_block_plan([pages], [64], 16, [0, 1, 2, 3])
+    shard = make_shards(g, 1, 16, 2)[0].to(cuda)
+    pool = B.ShardedPool.single(shard, g)
+    mover = B.PageMover(cuda)
+    cont = make_workers(g, [64], cuda)[0]                                   # [L, 2, 64, H, D]
+    layers = [torch.zeros(64, 2, g.n_kv_heads, g.head_dim, dtype=g.dtype, device=cuda) for _ in range(g.n_layers)]
+    mover.gather(pool, plan_c, cont)
+    mover.gather_nhd(pool, plan_b, layers)
+    torch.cuda.synchronize()
+    assert equal_bits(torch.stack(layers).permute(0, 2, 1, 3, 4), cont)
+
+
+def test_paged_worker_plan_is_validated(cuda):
+    g = GEOS["small"]
+    shard = torch.zeros(g.pool_shape(4), dtype=g.dtype, device=cuda)
+    pool = B.ShardedPool.single(shard, g)
+    mover = B.PageMover(cuda)
+    layers = [torch.zeros(32, 2, g.n_kv_heads, g.head_dim, dtype=g.dtype, device=cuda) for _ in range(g.n_layers)]
+    launches = N.lib().bikv_launch_count()
+    for table, status in [([[0, 16, 0, 17]], N.ERR_DST_RANGE), ([[4, 16, 0, 0]], N.ERR_PAGE_RANGE),
+                          ([[0, 0, 0, 0]], N.ERR_PLAN), ([[0, 16, 0, -16]], N.ERR_DST_RANGE)]:
+        with pytest.raises(B.BikvError) as e:
+            mover.gather_nhd(pool, Plan.from_table(np.array(table), 1), layers)
+        assert e.value.status == status
+    with pytest.raises(B.BikvError) as e:
+        mover.scatter_nhd(pool, Plan.from_table(np.array([[1, 16, 0, 0], [1, 16, 0, 16]]), 1), layers)
+    assert e.value.status == N.ERR_OVERLAP
+    with pytest.raises(ValueError):
+        mover.gather_nhd(pool, Plan.from_table(np.array([[0, 16, 0, 0]]), 1), layers[:-1])
+    assert N.lib().bikv_launch_count() == launches
+
+
+def test_pool_shard_in_pinned_host_memory(cuda):
+    """Host tier: a shard whose base is pinned (device-mapped) host memory, as the
+    reference's default pool placement (kvcache.py:38-43, read by its zero-copy kernel,
+    copy_kernel.cu:39-66).  The ld/st kernels read and write it in place over PCIe."""
+    g = GEOS["small"]
+    rng = np.random.default_rng(0)
+    per = 24
+    lists, tokens = random_plan(rng, g, 2 * per, 3, 90)
+    plan = build_plan([l.tolist() for l in lists], tokens.astype(np.int32), 16,
+                      item_request=np.arange(3, dtype=np.int32), n_requests=3)
+    recs = [tuple(r) for r in plan.table.tolist()]
+    shards_cpu = make_shards(g, 2, per, 8)
+    host_shard = shards_cpu[0].clone().pin_memory()          # shard 0 on the host
+    dev_shard = shards_cpu[1].to(cuda)                        # shard 1 in HBM
+    pool = B.ShardedPool([host_shard.data_ptr(), dev_shard.data_ptr()], per, g, device=cuda,
+                         keepalive=[host_shard, dev_shard])
+    mover = B.PageMover(cuda)
+    out = make_workers(g, tokens, cuda)
+    mover.gather(pool, plan, out, variant=N.VARIANT_LDST)
+    ref = make_workers(g, tokens)
+    O.gather(shards_cpu, g, recs, ref)
+    torch.cuda.synchronize()
+    for a, b in zip(out, ref):
+        assert equal_bits(a, b)
+    src = make_workers(g, tokens, fill="normal", seed=44)
+    mover.scatter(pool, plan, [t.to(cuda) for t in src], variant=N.VARIANT_LDST)
+    O.scatter(shards_cpu, g, recs, src)
+    torch.cuda.synchronize()
+    assert equal_bits(host_shard, shards_cpu[0]) and equal_bits(dev_shard, shards_cpu[1])

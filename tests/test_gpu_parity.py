@@ -243,3 +243,47 @@ def test_full_size_config1_properties(cuda):
     untouched = mask.nonzero().flatten()[:: 97]
     assert int(shard[untouched].view(torch.int16).ne(0).sum()) == 0
     mover.check_status()
+
+
+def test_empty_and_degenerate_plans(cuda):
+    """Empty plan, items without tokens, a single one-token page: no faults, no stray writes."""
+    g = SMALL
+    shard = torch.full(g.pool_shape(4), 3.0, dtype=g.dtype, device=cuda)
+    pool = B.ShardedPool.single(shard, g)
+    mover = B.PageMover(cuda)
+    out = make_workers(g, [16], cuda)
+    launches = N.lib().bikv_launch_count()
+    for plan in (build_plan([], [], 16), build_plan([[]], [0], 16), build_plan([[], []], [0, 0], 16)):
+        assert plan.n_pages == 0
+        mover.gather(pool, plan, out)
+        mover.scatter(pool, plan, out)
+    assert N.lib().bikv_launch_count() == launches
+    one = build_plan([[2]], [1], 16)
+    assert one.table.tolist() == [[2, 1, 0, 0]]
+    mover.gather(pool, one, out)
+    torch.cuda.synchronize()
+    assert float(out[0][:, :, 0].float().min()) == 3.0 and float(out[0][:, :, 1:].float().abs().max()) == 0.0
+    out[0].fill_(5.0)
+    mover.scatter(pool, one, out)
+    torch.cuda.synchronize()
+    page = shard[2]                                   # [L, 2, P, H, D]
+    assert float(page[:, :, 0].float().min()) == 5.0 and float(page[:, :, 1:].float().max()) == 3.0
+    assert float(shard[[0, 1, 3]].float().min()) == 3.0 and float(shard[[0, 1, 3]].float().max()) == 3.0
+
+
+def test_size_limits_are_refused_not_truncated(native):
+    """More chunks than the 32-bit item counter holds: refused on the host (needs no GPU
+    memory: the check precedes the launch)."""
+    import ctypes as C
+    g = N.Geometry(128, 8, 128, 16, 2, N.POOL_PAGED)          # 256 planes, 2 parts of 16 KiB each
+    pool = N.PoolDesc()
+    pool.shard_base[0] = 0x10000
+    pool.n_shards, pool.shard_rule, pool.pages_per_shard = 1, N.SHARD_MOD, 1 << 30
+    rc = native.bikv_gather(C.byref(pool), C.byref(g), C.c_void_p(0x1000), 1 << 23, C.c_void_p(0x2000), 1,
+                            N.VARIANT_LDST, None, None)
+    assert rc in (N.ERR_TOO_LARGE, N.ERR_CUDA)                # too many items, or no device on a CPU box
+    big = N.PoolDesc()
+    big.shard_base[0] = 0x10000
+    big.n_shards, big.shard_rule, big.pages_per_shard = 2, N.SHARD_MOD, 1 << 31
+    assert native.bikv_gather(C.byref(big), C.byref(g), C.c_void_p(0x1000), 1, C.c_void_p(0x2000), 1,
+                              N.VARIANT_LDST, None, None) == N.ERR_TOO_LARGE

@@ -94,7 +94,7 @@ class ClockSampler:
             self.out = open(self.path, "w")
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", ident, f"--query-gpu=timestamp,{CLOCK_FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "50"], stdout=self.out, stderr=subprocess.DEVNULL)
+                 "-lms", "20"], stdout=self.out, stderr=subprocess.DEVNULL)
         except Exception:  # noqa: BLE001
             self.proc = None
         self.t0 = self.t1 = None
@@ -532,27 +532,30 @@ def main():
     stream = torch.cuda.current_stream(dev)
     nhd = args.worker_layout == "nhd"
     if nhd:
+        # Side measurement: the worker's KV is paged, one [slot, kv, head, dim] tensor per layer.
+        import numpy as np
         from bikv_b200.plan import build_block_plan
-        import numpy as _np
-        blocks = _np.random.default_rng(7).permutation(w.n_pages)
+        blocks = np.random.default_rng(7).permutation(w.n_pages)
         plan = build_block_plan(w.flat(), w.request_tokens.astype("int32"), geom.page_tokens, blocks)
         layers = [torch.zeros((w.n_pages * geom.page_tokens, 2, geom.n_kv_heads, geom.head_dim), dtype=geom.dtype,
                               device=dev) for _ in range(geom.n_layers)]
+        tensors = []
+        args.no_e2e = True
 
-        real_mover = mover
+        def launch_gather():
+            mover.gather_nhd(pool, plan, layers, validate=False)
 
-        class _Nhd:   # same two calls as the contiguous path, on the paged worker KV
-            @staticmethod
-            def gather_dev(pool, *_):
-                real_mover.gather_nhd(pool, plan, layers, validate=False)
-
-            @staticmethod
-            def scatter_dev(pool, *_):
-                real_mover.scatter_nhd(pool, plan, layers, validate=False)
-        tensors, d_recs, d_reqs = [], None, None
+        def launch_scatter():
+            mover.scatter_nhd(pool, plan, layers, validate=False)
     else:
         tensors = [torch.zeros(geom.worker_shape(int(t)), dtype=geom.dtype, device=dev) for t in w.request_tokens]
         d_recs, d_reqs = mover.upload(plan, geom, tensors)
+
+        def launch_gather():
+            mover.gather_dev(pool, d_recs, d_reqs)
+
+        def launch_scatter():
+            mover.scatter_dev(pool, d_recs, d_reqs)
 
     def barrier():
         if multi:
@@ -560,9 +563,6 @@ def main():
 
     do_g, do_s = args.only in ("both", "gather"), args.only in ("both", "scatter")
     n_dirs = int(do_g) + int(do_s)
-    if nhd:
-        mover = _Nhd
-        args.no_e2e = True
 
     def phase_end():
         """N > 1: ranks move data the same way at the same time (all gather, then all
@@ -575,15 +575,15 @@ def main():
 
     def step_resident():
         if do_g:
-            mover.gather_dev(pool, d_recs, d_reqs)
+            launch_gather()
             phase_end()
         if do_s:
-            mover.scatter_dev(pool, d_recs, d_reqs)
+            launch_scatter()
             phase_end()
 
     flat_begin = w.flat()
     item_tokens = w.request_tokens.astype("int32")
-    item_req = __import__("numpy").arange(w.n_requests, dtype="int32")
+    item_req = list(range(w.n_requests))
 
     def step_e2e():
         p = build_plan(flat_begin, item_tokens, geom.page_tokens, item_request=item_req, n_requests=w.n_requests)
@@ -613,13 +613,13 @@ def main():
     for k in range(args.steps):
         ev[k][0].record(stream)
         if do_g:
-            mover.gather_dev(pool, d_recs, d_reqs)
+            launch_gather()
         ev[k][1].record(stream)
         if do_g:
             phase_end()
         ev[k][3].record(stream)
         if do_s:
-            mover.scatter_dev(pool, d_recs, d_reqs)
+            launch_scatter()
         ev[k][2].record(stream)
         if do_s:
             phase_end()
@@ -632,8 +632,6 @@ def main():
     elapsed_ms = t_begin.elapsed_time(t_end)
     gather_ms = [e[0].elapsed_time(e[1]) for e in ev]
     scatter_ms = [e[3].elapsed_time(e[2]) for e in ev]
-    if nhd:
-        mover = real_mover
     mover.check_status()
 
     # ---- end to end through the Python API, host-resident plan ----

@@ -53,3 +53,38 @@ def test_flat_copy_not_slower_than_reference_kernel(cuda, page_size, n_pages):
           f"reference kernel {nbytes / t_ref / 1e6:.1f} GB/s ({t_ref:.3f} ms), "
           f"bikv_copy_pages_flat {nbytes / t_new / 1e6:.1f} GB/s ({t_new:.3f} ms), x{t_ref / t_new:.2f}")
     assert t_new <= t_ref * 1.05
+
+
+def test_gather_against_torch_gpu_ops(cuda):
+    """The same gather written with stock torch ops on the GPU (index_select of whole pages,
+    permute to [layer, kv, token, head, dim], contiguous) against bikv_gather, config-1
+    geometry, 2,048 whole pages into one tensor.  Results must agree bit for bit; both rates
+    are printed."""
+    from bikv_b200.plan import build_plan
+
+    g = B.GEO_B
+    pool_pages, n = 4096, 2048
+    shard = torch.randn(g.pool_shape(pool_pages), device=cuda, dtype=torch.float32).to(g.dtype)
+    ids = torch.from_numpy(np.random.default_rng(1).permutation(pool_pages)[:n].astype(np.int64)).to(cuda)
+    plan = build_plan([ids.tolist()], [n * 16], 16)
+    out = torch.zeros(g.worker_shape(n * 16), dtype=g.dtype, device=cuda)
+    mover = B.PageMover(cuda)
+    pool = B.ShardedPool.single(shard, g)
+    d_recs, d_reqs = mover.upload(plan, g, out)
+
+    def torch_ops():
+        pages = shard.index_select(0, ids)                                    # [n, L, 2, P, H, D]
+        return pages.permute(1, 2, 0, 3, 4, 5).reshape(g.n_layers, 2, n * 16, g.n_kv_heads, g.head_dim).contiguous()
+
+    want = torch_ops()
+    mover.gather_dev(pool, d_recs, d_reqs)
+    torch.cuda.synchronize()
+    assert torch.equal(out.view(torch.int16), want.view(torch.int16))
+    del want
+    t_torch = _time(torch_ops)
+    t_new = _time(lambda: mover.gather_dev(pool, d_recs, d_reqs))
+    nbytes = n * g.page_bytes
+    print(f"\n[gather {n} pages = {nbytes / 2**30:.2f} GiB] torch index_select+permute+contiguous "
+          f"{nbytes / t_torch / 1e6:.1f} GB/s ({t_torch:.3f} ms), bikv_gather {nbytes / t_new / 1e6:.1f} GB/s "
+          f"({t_new:.3f} ms), x{t_torch / t_new:.2f}")
+    assert t_new <= t_torch

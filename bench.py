@@ -383,12 +383,13 @@ def run_config4(ctx):
     result = None
     if not is_shard:
         import ctypes as C
-        bases = []
+        bases, imported = [], []
         for h in handles[:n_shards]:
             out = C.c_void_p()
             N.check(lib.bikv_pool_import(h[0], int(h[1]), C.byref(out)), "bikv_pool_import")
             bases.append(int(out.value))
-        pool = B.ShardedPool(bases, args.pool_pages, geom, rule=N.SHARD_BLOCK, device=dev, imported=list(bases))
+            imported.append((int(out.value), int(h[1])))
+        pool = B.ShardedPool(bases, args.pool_pages, geom, rule=N.SHARD_BLOCK, device=dev, imported=imported)
         me = rank - n_shards
         wl = PrefixReuseWorkload(seed=0, n_workers=n_workers, n_requests=args.c4_requests, batch=64)
         co = (NativePrefixCacheCoordinator(n_shards, args.pool_pages, geom.page_tokens) if args.c4_planner == "native"

@@ -126,7 +126,7 @@ SIGNATURES = {
     "bikv_enable_peer": (C.c_int, [C.c_int, C.c_int]),
     "bikv_pool_export": (C.c_int, [_P, C.c_char_p, C.POINTER(C.c_int64)]),
     "bikv_pool_import": (C.c_int, [C.c_char_p, C.c_int64, C.POINTER(_P)]),
-    "bikv_pool_close": (C.c_int, [_P]),
+    "bikv_pool_close": (C.c_int, [_P, C.c_int64]),
     # include/bikv_pm.h
     "bikv_pm_create": (_P, [C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_uint64]),
     "bikv_pm_destroy": (None, [_P]),

@@ -755,24 +755,14 @@ int bikv_pool_import(const unsigned char handle[64], int64_t offset, void** ptr)
   return BIKV_OK;
 }
 
-namespace {
-std::mutex g_imp_mu;
-}
-
-int bikv_pool_close(void* ptr) {
-  if (!ptr) return BIKV_ERR_BAD_ARG;
-  // cudaIpcCloseMemHandle wants the mapping's base: recover it the same way
-  // export does.
-  typedef int (*get_range_fn)(unsigned long long*, size_t*, unsigned long long);
-  void* fn = nullptr;
-  cudaDriverEntryPointQueryResult qres;
-  BIKV_CUDA(cudaGetDriverEntryPoint("cuMemGetAddressRange", &fn, cudaEnableDefault, &qres));
-  if (!fn || qres != cudaDriverEntryPointSuccess) return BIKV_ERR_PEER;
-  unsigned long long base = 0;
-  size_t size = 0;
-  if (((get_range_fn)fn)(&base, &size, (unsigned long long)(uintptr_t)ptr) != 0) return BIKV_ERR_PEER;
-  std::lock_guard<std::mutex> lk(g_imp_mu);
-  BIKV_CUDA(cudaIpcCloseMemHandle((void*)(uintptr_t)base));
+int bikv_pool_close(void* ptr, int64_t offset) {
+  if (!ptr || offset < 0) return BIKV_ERR_BAD_ARG;
+  // cudaIpcCloseMemHandle wants the base address that cudaIpcOpenMemHandle returned.
+  cudaError_t e = cudaIpcCloseMemHandle((char*)ptr - offset);
+  if (e != cudaSuccess) {
+    cuda_fail(e);
+    return BIKV_ERR_PEER;
+  }
   return BIKV_OK;
 }
 

@@ -36,7 +36,7 @@ class ShardedPool:
 
     def __init__(self, bases: Sequence[int], pages_per_shard: int, geom: KVGeometry,
                  rule: int = N.SHARD_MOD, device: Optional[torch.device] = None,
-                 keepalive: Optional[list] = None, imported: Optional[List[int]] = None):
+                 keepalive: Optional[list] = None, imported: Optional[List[tuple]] = None):
         if not 1 <= len(bases) <= N.MAX_SHARDS:
             raise ValueError(f"1..{N.MAX_SHARDS} shards supported, got {len(bases)}")
         self.bases = [int(b) for b in bases]
@@ -115,7 +115,7 @@ class ShardedPool:
             out = C.c_void_p()
             N.check(N.lib().bikv_pool_import(h[0], int(h[1]), C.byref(out)), "bikv_pool_import")
             bases.append(int(out.value))
-            imported.append(int(out.value))
+            imported.append((int(out.value), int(h[1])))
         per = own_shard.numel() * own_shard.element_size() // geom.page_bytes
         return cls(bases, per, geom, rule, own_shard.device, keepalive=[own_shard], imported=imported)
 
@@ -135,6 +135,7 @@ class ShardedPool:
         return cls.from_handles(handles, rank, own_shard, geom, rule, importer=importer)
 
     def close(self) -> None:
-        for p in self._imported:
-            N.lib().bikv_pool_close(C.c_void_p(p))
-        self._imported = []
+        """Unmaps the shards opened from IPC handles (entries are (mapped pointer, offset))."""
+        imported, self._imported = self._imported, []
+        for ptr, offset in imported:
+            N.check(N.lib().bikv_pool_close(C.c_void_p(ptr), offset), "bikv_pool_close")

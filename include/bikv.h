@@ -291,11 +291,11 @@ int bikv_enable_peer(int device, int peer);
  * POSIX shm block or the staging ring: export yields the 64-byte CUDA IPC
  * handle of the allocation that contains `ptr` plus ptr's offset inside it;
  * import maps it in another process and returns the mapped address of `ptr`.
- * bikv_pool_close takes the pointer import returned.
+ * bikv_pool_close takes the pointer import returned and the same offset.
  */
 int bikv_pool_export(void* ptr, unsigned char handle[64], int64_t* offset);
 int bikv_pool_import(const unsigned char handle[64], int64_t offset, void** ptr);
-int bikv_pool_close(void* ptr);
+int bikv_pool_close(void* ptr, int64_t offset);
 
 #ifdef __cplusplus
 }

@@ -596,6 +596,18 @@ def main():
             phase_end()
         mover.check_status()          # 16-byte device->host read, synchronises the step
 
+    def shard_checksum():
+        """Bit-level checksum of this rank's shard.  A step scatters back exactly what it
+        gathered, so the pool must come out of the whole run unchanged (checked after the
+        timed regions, on every rank, at full size)."""
+        words = shard.view(-1).view(torch.int32)          # every geometry's page is a multiple of 4 bytes
+        total = torch.zeros((), dtype=torch.int64, device=dev)
+        step = 1 << 27                                     # 1 GiB of int64 scratch per chunk
+        for at in range(0, words.numel(), step):
+            total += words[at:at + step].sum(dtype=torch.int64)
+        return int(total)
+
+    checksum_before = shard_checksum() if args.only == "both" else None
     sampler = ClockSampler(local_rank) if rank == 0 else None
     for _ in range(args.warmup):
         step_resident()
@@ -653,6 +665,18 @@ def main():
 
     clocks = sampler.finish() if sampler else None
 
+    verified = None
+    if checksum_before is not None:
+        barrier()
+        ok = float(shard_checksum() == checksum_before)
+        if multi:
+            t_ok = torch.tensor([ok], dtype=torch.float64)
+            dist.all_reduce(t_ok, op=dist.ReduceOp.MIN)
+            ok = float(t_ok[0])
+        verified = bool(ok)
+        if not verified:
+            raise SystemExit("bench.py: the pool changed across gather->scatter round trips (bits differ)")
+
     # ---- max over ranks ----
     payload = w.payload_bytes
     pages = w.n_pages
@@ -703,6 +727,7 @@ def main():
             "scaling": "weak", "vs_baseline": None, "dtype": "u16", "data": "synthetic",
             "config": config_dict(args, w), "pages_per_s": n_dirs * total_pages * args.steps / secs,
             "roofline": roofline, "gpu_launches": total_launches, "clocks": clocks,
+            "verified": {"pool_unchanged_after_round_trips": verified},
         }
         if e2e:
             line["e2e"] = {"value": n_dirs * total_payload * args.steps / e2e["seconds"] / 1e9, "unit": UNIT,

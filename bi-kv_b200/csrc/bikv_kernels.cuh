@@ -1,13 +1,19 @@
 // Device code of the KV-page data path: pure data movement, no arithmetic.
 //
-// Three kernels cover the paged pool layout and the flat reference copy:
-//   k_paged_ldst   one warp per (page, plane, part) chunk, 16-byte ld/st
-//   k_paged_bulk   one issuing thread per CTA, cp.async.bulk ring
-//                  global -> shared -> global (no multicast, no tensor map)
-//   k_flat         dst[dst_off[i]+e] = src[src_off[i]+e], any alignment
-// and one covers the reference's token-major pool:
-//   k_token_major  shared-memory transpose of [dim][head][layer][kv] token rows
-//                  into [layer][kv][token][head][dim] (and back)
+// Paged pool (page = [layer][kv][token][head][dim]):
+//   k_paged_ldst      one warp per (page, plane, part) chunk, 16-byte ld/st
+//   k_paged_bulk      one issuing thread per CTA, cp.async.bulk ring
+//                     global -> shared -> global (no tensor map; plain, CTA-local
+//                     bulk copies only)
+//   k_paged_nhd       same chunks against a worker whose KV is paged per layer
+//                     ([slot][kv][head][dim])
+// Token-major pool of the reference (token = [dim][head][layer][kv]):
+//   k_token_major16v  2-byte elements: swizzled 16-byte shared-memory units,
+//                     cp.async double buffering on gather
+//   k_token_major16   2-byte elements, any layer count: 4-byte units, odd pitch
+//   k_token_major<T>  1- and 4-byte elements
+// Flat reference copy:
+//   k_flat            dst[dst_off[i]+e] = src[src_off[i]+e], any alignment
 //
 // A "plane" is one (layer, kv) pair; in the paged layout a page holds
 // 2*n_layers planes of page_tokens*heads*dim elements each, so a plane of a

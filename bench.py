@@ -60,6 +60,10 @@ def parse_args():
                     help="side measurement: time one direction only (all ranks then move data the same way)")
     ap.add_argument("--worker-layout", default="contiguous", choices=["contiguous", "nhd"],
                     help="nhd = the worker's paged KV, one [slot, kv, head, dim] tensor per layer (side measurement)")
+    ap.add_argument("--gather-mode", default="pull", choices=["pull", "push"],
+                    help="N > 1: pull = the worker's GPU reads remote pages (loads over NVLink; the default, and the "
+                         "faster one: 7.55 against 8.28 ms per gather on 2 GPUs); push = the GPU that owns a page "
+                         "writes it into the worker's tensor, as the reference's shard does on SEND (side measurement)")
     ap.add_argument("--small", action="store_true", help="profiling-sized case (2,048-page pool, 8 requests)")
     ap.add_argument("--tune", action="append", default=[], metavar="KNOB=VALUE")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -207,12 +211,15 @@ def config_dict(args, w):
     c = {"workload": name, "pool_pages_per_gpu": args.pool_pages, "requests_per_gpu": args.requests,
          "request_lengths": "lognormal(median 2048, sigma 0.8) clipped to [64, 8192]",
          "step": "gather all requests + scatter them back" + ("" if args.gpus == 1 else
-                                                                  "; ranks phase-aligned by a host barrier after each direction"),
+                                                                  "; ranks phase-aligned by a host barrier after each direction"
+                                                                  f"; gather by {args.gather_mode}"),
          "l2": "inputs larger than L2 (payload per launch is ~10 GB against 126 MB of L2)"}
     if args.small:
         c["workload"] += " [SMALL profiling case]"
     if args.only != "both":
         c["workload"] += f" [SIDE MEASUREMENT: {args.only} only]"
+    if args.gather_mode != "pull" and args.gpus > 1:
+        c["workload"] += " [SIDE MEASUREMENT: gather pushed by the pages' owner]"
     if args.worker_layout != "contiguous":
         c["workload"] += " [SIDE MEASUREMENT: worker KV paged, one [slot, kv, head, dim] tensor per layer]"
     if args.pages_from != "all":
@@ -227,6 +234,20 @@ def config_dict(args, w):
 
 
 # --------------------------------------------------------------------------- additional workloads
+def _arena_offsets(geom, tokens_list):
+    """Element offsets of worker tensors laid one after another, each start 128-element aligned."""
+    out, at = [], 0
+    for t in tokens_list:
+        out.append(at)
+        at += (geom.token_elems * int(t) + 127) // 128 * 128
+    return out
+
+
+def _arena_elems(geom, tokens_list):
+    offs = _arena_offsets(geom, tokens_list)
+    return offs[-1] + (geom.token_elems * int(tokens_list[-1]) + 127) // 128 * 128 if len(offs) else 0
+
+
 def _carve(arena, geom, tokens_list):
     """Worker tensors [layer, kv, T, head, dim] laid one after another in a flat arena."""
     import torch
@@ -523,8 +544,9 @@ def main():
     W.fill_normal_(shard, seed=1234 + rank)
     if multi:
         pool = B.ShardedPool.exchange(shard, geom, group=cpu_group)
-        w = W.config2(rank, world, seed=0, pages_per_shard=args.pool_pages, n_requests=args.requests, geom=geom,
-                      pages_from=args.pages_from)
+        all_w = [W.config2(r, world, seed=0, pages_per_shard=args.pool_pages, n_requests=args.requests, geom=geom,
+                           pages_from=args.pages_from) for r in range(world)]
+        w = all_w[rank]
     else:
         pool = B.ShardedPool.single(shard, geom)
         w = W.config1(seed=0, n_pages=args.pool_pages, n_requests=args.requests, geom=geom)
@@ -549,7 +571,13 @@ def main():
         def launch_scatter():
             mover.scatter_nhd(pool, plan, layers, validate=False)
     else:
-        tensors = [torch.zeros(geom.worker_shape(int(t)), dtype=geom.dtype, device=dev) for t in w.request_tokens]
+        push = multi and args.gather_mode == "push"
+        if push:
+            # Worker tensors come out of one arena per rank so that one IPC handle maps them all.
+            arena = torch.zeros(_arena_elems(geom, w.request_tokens), dtype=geom.dtype, device=dev)
+            tensors = _carve(arena, geom, w.request_tokens)
+        else:
+            tensors = [torch.zeros(geom.worker_shape(int(t)), dtype=geom.dtype, device=dev) for t in w.request_tokens]
         d_recs, d_reqs = mover.upload(plan, geom, tensors)
 
         def launch_gather():
@@ -557,6 +585,41 @@ def main():
 
         def launch_scatter():
             mover.scatter_dev(pool, d_recs, d_reqs)
+
+        if push:
+            import ctypes as C
+            import numpy as np
+            from bikv_b200.plan import Plan
+            from bikv_b200.push import split_plans_by_owner
+            handles = [None] * world
+            dist.all_gather_object(handles, B.ShardedPool.export_handle(arena), group=cpu_group)
+            arena_base, arena_maps = [], []
+            for r, h in enumerate(handles):
+                if r == rank:
+                    arena_base.append(arena.data_ptr())
+                    continue
+                out = C.c_void_p()
+                N.check(lib.bikv_pool_import(h[0], int(h[1]), C.byref(out)), "bikv_pool_import")
+                arena_base.append(int(out.value))
+                arena_maps.append((int(out.value), int(h[1])))
+            # Rows of every worker's plan whose page lives on this GPU; bases of every worker's
+            # tensors as mapped here.
+            push_table = split_plans_by_owner([x.plan().table for x in all_w], [x.n_requests for x in all_w], rank,
+                                              world, args.pool_pages)
+            push_reqs = torch.empty((sum(x.n_requests for x in all_w), 2), dtype=torch.int64).pin_memory()
+            at = 0
+            for r, x in enumerate(all_w):
+                for off, t in zip(_arena_offsets(geom, x.request_tokens), x.request_tokens):
+                    push_reqs[at, 0] = arena_base[r] + off * geom.elt_bytes
+                    push_reqs[at, 1] = int(t)
+                    at += 1
+            d_push_recs = torch.from_numpy(push_table).to(dev)
+            d_push_reqs = push_reqs.to(dev)
+            own = (push_table[:, 2] >= rank * args.requests) & (push_table[:, 2] < (rank + 1) * args.requests)
+            pushed_remote_bytes = int(push_table[~own, 1].sum()) * geom.bytes_per_token
+
+            def launch_gather():   # noqa: F811  (the owner-side form replaces the pull)
+                mover.gather_dev(pool, d_push_recs, d_push_reqs)
 
     def barrier():
         if multi:
@@ -587,9 +650,14 @@ def main():
     item_req = list(range(w.n_requests))
 
     def step_e2e():
-        p = build_plan(flat_begin, item_tokens, geom.page_tokens, item_request=item_req, n_requests=w.n_requests)
+        p = build_plan(flat_begin, item_tokens, geom.page_tokens, item_request=item_req, n_requests=w.n_requests,
+                       transient=True)
         if do_g:
-            mover.gather(pool, p, tensors)
+            if multi and args.gather_mode == "push" and not nhd:
+                # the shard's share of the batch as the coordinator would deliver it: page records
+                mover.gather_table(pool, Plan.from_table(push_table, len(push_reqs), transient=True), push_reqs)
+            else:
+                mover.gather(pool, p, tensors)
             phase_end()
         if do_s:
             mover.scatter(pool, p, tensors)
@@ -718,7 +786,10 @@ def main():
         if multi:
             remote = w.remote_fraction(rank)
             nv = remote * payload / (statistics.mean(gather_ms) / 1e3) / 1e9
-            roofline["nvlink"] = {"remote_fraction": remote, "gather_ingress_GBps_per_gpu": nv,
+            if args.gather_mode == "push" and not nhd:
+                nv = pushed_remote_bytes / (statistics.mean(gather_ms) / 1e3) / 1e9
+            roofline["nvlink"] = {"remote_fraction": remote, "gather_mode": args.gather_mode,
+                                  "gather_ingress_GBps_per_gpu": nv,
                                   "frac_of_770_measured": nv / 770.0, "frac_of_900_nominal": nv / 900.0,
                                   "scatter_egress_GBps_per_gpu": remote * payload / (statistics.mean(scatter_ms) / 1e3) / 1e9}
         line = {
@@ -744,6 +815,9 @@ def main():
     if multi:
         barrier()
         pool.close()
+        if args.gather_mode == "push" and not nhd:
+            for ptr, off in arena_maps:
+                N.check(lib.bikv_pool_close(C.c_void_p(ptr), off), "bikv_pool_close")
         dist.destroy_process_group()
 
 

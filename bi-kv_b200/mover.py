@@ -113,6 +113,38 @@ class PageMover:
         """Worker tensors -> pool pages (inverse map of :meth:`gather`)."""
         self._run_h(N.lib().bikv_scatter_h, pool, plan, tensors, validate, variant, stream)
 
+    def gather_table(self, pool: ShardedPool, plan: Plan, request_table: torch.Tensor, *, validate: bool = True,
+                     variant: Optional[int] = None, stream=None) -> None:
+        """:meth:`gather` with a ready request table: host int64 ``[n, 2]`` rows of (base pointer,
+        tokens), pinned for an asynchronous upload.  For worker tensors that are not torch tensors
+        of this process -- e.g. another GPU's tensors mapped through an IPC handle, when the
+        owner of the pages pushes them (``push.py``).  The table must stay unchanged until the
+        stream has passed the call."""
+        self._run_table(N.lib().bikv_gather_h, pool, plan, request_table, validate, variant, stream)
+
+    def scatter_table(self, pool: ShardedPool, plan: Plan, request_table: torch.Tensor, *, validate: bool = True,
+                      variant: Optional[int] = None, stream=None) -> None:
+        self._run_table(N.lib().bikv_scatter_h, pool, plan, request_table, validate, variant, stream)
+
+    def _run_table(self, fn, pool, plan, request_table, validate, variant, stream) -> None:
+        if plan.n_pages == 0:
+            return
+        if request_table.dtype != torch.int64 or request_table.dim() != 2 or request_table.shape[1] != 2 \
+                or not request_table.is_contiguous() or request_table.is_cuda:
+            raise ValueError("request_table must be a contiguous host int64 [n, 2] tensor")
+        n = request_table.shape[0]
+        scratch = self._scratch_for(plan.n_pages, n)
+        g = pool.geom.native()
+        rc = fn(C.byref(pool.desc), C.byref(g), C.c_void_p(plan.host_ptr), plan.n_pages,
+                C.c_void_p(request_table.data_ptr()), n, C.c_void_p(scratch.data_ptr()), scratch.numel(),
+                int(validate), self.variant if variant is None else variant,
+                C.c_void_p(self.status.data_ptr()), C.c_void_p(self._stream(stream)))
+        N.check(rc, fn.__name__)
+        ev = torch.cuda.Event()
+        ev.record(stream if stream is not None else torch.cuda.current_stream(self.device))
+        self._inflight = [(e, p) for e, p in self._inflight if not e.query()]
+        self._inflight.append((ev, (plan, request_table)))
+
     # -- device-plan path --------------------------------------------------
     def upload(self, plan: Plan, geom: KVGeometry, tensors: Tensors):
         """Copies a plan and its request table to fresh device tensors (for repeated

@@ -25,9 +25,9 @@ REC_DTYPE = np.dtype([("page_id", "<i4"), ("valid_tokens", "<i4"), ("request", "
 
 class _PinnedRows:
     """Recycles pinned int32 [rows, 4] buffers: pinning host memory costs far more than
-    building a plan, so buffers of dropped plans are handed out again.  A buffer comes
-    back only when its ``Plan`` is garbage-collected; ``PageMover`` keeps every plan it
-    has launched alive until the stream has passed the upload."""
+    building a plan, so buffers of dropped TRANSIENT plans are handed out again.  A buffer
+    comes back only when its ``Plan`` is garbage-collected; ``PageMover`` keeps every plan
+    it has launched alive until the stream has passed the upload."""
 
     def __init__(self):
         self._free: list = []
@@ -61,18 +61,23 @@ def _pinned_i32(n_rows: int, cols: int) -> torch.Tensor:
 class Plan:
     """Page records in host memory (pinned when a GPU is present)."""
 
-    def __init__(self, recs: torch.Tensor, n_pages: int, request_tokens: np.ndarray):
+    def __init__(self, recs: torch.Tensor, n_pages: int, request_tokens: np.ndarray, transient: bool = False):
         self._store = recs                      # int32 [cap, 4], keeps the memory alive
         self.n_pages = int(n_pages)
         self.request_tokens = request_tokens    # int64 [n_requests]
+        self.transient = transient              # see __del__
 
     def __del__(self):
+        # Only a plan marked transient gives its pinned buffer back for reuse: its creator
+        # promised that no ``table`` / ``recs`` view outlives it (numpy views do not keep the
+        # plan alive, so recycling under a live view would change what the view shows).
         store = self.__dict__.pop("_store", None)
-        if store is not None and _pinned is not None:
-            try:
-                _pinned.put(store)
-            except Exception:  # noqa: BLE001  (interpreter shutdown)
-                pass
+        if store is None or not self.__dict__.get("transient") or _pinned is None:
+            return
+        try:
+            _pinned.put(store)
+        except Exception:  # noqa: BLE001  (interpreter shutdown)
+            pass
 
     @property
     def n_requests(self) -> int:
@@ -97,7 +102,7 @@ class Plan:
         return int(self.request_tokens.sum())
 
     @classmethod
-    def from_table(cls, table: np.ndarray, n_requests: Optional[int] = None) -> "Plan":
+    def from_table(cls, table: np.ndarray, n_requests: Optional[int] = None, transient: bool = False) -> "Plan":
         table = np.ascontiguousarray(table, dtype=np.int32).reshape(-1, 4)
         store = _pinned_i32(len(table), 4)
         store.numpy()[: len(table)] = table
@@ -106,7 +111,7 @@ class Plan:
         ok = (table[:, 2] >= 0) & (table[:, 2] < nreq)   # bad rows are the validator's business
         if ok.any():
             np.maximum.at(req_tokens, table[ok, 2], (table[ok, 1] + table[ok, 3]).astype(np.int64))
-        return cls(store, len(table), req_tokens)
+        return cls(store, len(table), req_tokens, transient)
 
 
 def flatten_page_lists(cache_pages_list: Iterable[Sequence[int]]):
@@ -121,7 +126,7 @@ def flatten_page_lists(cache_pages_list: Iterable[Sequence[int]]):
 
 
 def build_plan(cache_pages_list, item_tokens, page_tokens: int, *, item_request=None,
-               n_requests: int = 1, item_shard=None, pages_per_shard: int = 0) -> Plan:
+               n_requests: int = 1, item_shard=None, pages_per_shard: int = 0, transient: bool = False) -> Plan:
     """Builds the records for a batch of items.
 
     ``cache_pages_list[j]`` are the pool pages of item ``j`` and ``item_tokens[j]``
@@ -130,7 +135,8 @@ def build_plan(cache_pages_list, item_tokens, page_tokens: int, *, item_request=
     the worker tensor the item lands in (default: all in tensor 0, one packed
     buffer as in the reference); offsets run per tensor in item order.
     ``item_shard`` turns shard-local page numbers into global ids for
-    ``SHARD_BLOCK`` pools.
+    ``SHARD_BLOCK`` pools.  ``transient=True``: the caller keeps no ``table`` / ``recs`` view
+    beyond the plan's life, so its pinned buffer may be reused by later plans.
     """
     if isinstance(cache_pages_list, tuple) and len(cache_pages_list) == 2:
         flat, begin = cache_pages_list
@@ -153,7 +159,7 @@ def build_plan(cache_pages_list, item_tokens, page_tokens: int, *, item_request=
                                   int(n_requests), C.c_void_p(store.data_ptr()), n_pages)
     if got < 0:
         raise N.BikvError(int(got), "bikv_plan_build")
-    return Plan(store, int(got), req_tokens)
+    return Plan(store, int(got), req_tokens, transient)
 
 
 def plan_from_combined_task(task, page_tokens: int, *, pages_per_shard: int = 0,
@@ -167,7 +173,7 @@ def plan_from_combined_task(task, page_tokens: int, *, pages_per_shard: int = 0,
         pages, cache_worker = task.cache_pages_list, task.cache_worker
         tokens = [p.token_num for p in task.id_token_pair]
     shard = [cache_worker] * len(tokens) if block_sharded else None
-    return build_plan(pages, tokens, page_tokens, item_shard=shard, pages_per_shard=pages_per_shard)
+    return build_plan(pages, tokens, page_tokens, item_shard=shard, pages_per_shard=pages_per_shard, transient=True)
 
 
 def build_block_plan(cache_pages_list, item_tokens, page_tokens: int, block_ids, *, item_shard=None,

@@ -181,3 +181,100 @@ def test_nvlink_ceilings_report():
     for k, v in results.items():
         print(f"[nvlink ceiling] contiguous {k}: {v:.1f} GB/s per direction")
     assert all(v > 100 for v in results.values())
+
+
+PUSH_SCRIPT = """
+import ctypes as C, os, sys
+sys.path.insert(0, {root!r})
+sys.path.insert(0, os.path.join({root!r}, "tests"))
+import numpy as np, torch, torch.distributed as dist
+import bikv_b200 as B
+from bikv_b200 import _native as N, multi
+from bikv_b200.geometry import KVGeometry
+from bikv_b200.plan import Plan, build_plan
+from bikv_b200.pool import ShardedPool
+from bikv_b200.push import split_plans_by_owner
+from oracle import bikv_oracle as O
+from helpers import equal_bits, make_shards, make_workers
+
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(rank)
+dev = torch.device(f"cuda:{{rank}}")
+dist.init_process_group("gloo", init_method="tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+g = KVGeometry(4, 2, 128, 16, torch.bfloat16)
+per = 32
+shards_cpu = make_shards(g, world, per, 5, fill="bits")
+mine = shards_cpu[rank].to(dev)
+pool = ShardedPool.exchange(mine, g)
+perm = np.random.default_rng(0).permutation(world * per)
+tokens = np.array([100, 37, 16 * 8])
+counts = (tokens + 15) // 16
+tables = []
+for r in range(world):                      # every rank can write down every worker's plan
+    share, lists, at = perm[r * per:(r + 1) * per], [], 0
+    for c in counts:
+        lists.append(share[at:at + c].tolist()); at += c
+    tables.append(build_plan(lists, tokens.astype(np.int32), 16, item_request=[0, 1, 2], n_requests=3).table.copy())
+# worker tensors of this rank in one arena, mapped by everyone
+elems = [g.token_elems * int(t) for t in tokens]
+offs = np.concatenate([[0], np.cumsum(elems)[:-1]])
+arena = torch.zeros(int(sum(elems)), dtype=g.dtype, device=dev)
+handles = [None] * world
+dist.all_gather_object(handles, ShardedPool.export_handle(arena))
+bases, maps = [], []
+for r, h in enumerate(handles):
+    if r == rank:
+        bases.append(arena.data_ptr()); continue
+    out = C.c_void_p()
+    N.check(N.lib().bikv_pool_import(h[0], int(h[1]), C.byref(out)))
+    bases.append(int(out.value)); maps.append((int(out.value), int(h[1])))
+reqs = torch.empty((3 * world, 2), dtype=torch.int64).pin_memory()
+for r in range(world):
+    for i in range(3):
+        reqs[3 * r + i, 0] = bases[r] + int(offs[i]) * 2
+        reqs[3 * r + i, 1] = int(tokens[i])
+push = split_plans_by_owner(tables, [3] * world, rank, world, per)
+mover = B.PageMover(dev)
+for variant in (N.VARIANT_LDST, N.VARIANT_BULK):
+    arena.zero_()
+    torch.cuda.synchronize()
+    multi.host_barrier(timeout_s=60)
+    mover.gather_table(pool, Plan.from_table(push, 3 * world), reqs, variant=variant)     # owner pushes
+    torch.cuda.synchronize()
+    mover.check_status()
+    multi.host_barrier(timeout_s=60)              # every owner's stores have landed
+    ref = make_workers(g, tokens)
+    O.gather(shards_cpu, g, [tuple(x) for x in tables[rank].tolist()], ref)
+    for i in range(3):
+        got = arena[int(offs[i]):int(offs[i]) + elems[i]].view(g.worker_shape(int(tokens[i])))
+        assert equal_bits(got, ref[i]), "push gather mismatch, request %d" % i
+    multi.host_barrier(timeout_s=60)
+remote = int((push[:, 2] // 3 != rank).sum())
+print("RANK_OK", rank, "pushed", remote, "remote pages of", len(push))
+multi.host_barrier(timeout_s=60)
+for ptr, off in maps:
+    N.check(N.lib().bikv_pool_close(C.c_void_p(ptr), off))
+pool.close()
+dist.destroy_process_group()
+"""
+
+
+def test_owner_push_gather_across_processes():
+    _need_gpus(2)
+    world = min(torch.cuda.device_count(), 4)
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    script = textwrap.dedent(PUSH_SCRIPT).format(root=ROOT, port=port)
+    procs = []
+    for r in range(world):
+        env = dict(os.environ, RANK=str(r), WORLD_SIZE=str(world))
+        procs.append(subprocess.Popen([sys.executable, "-c", script], env=env, stdout=subprocess.PIPE,
+                                      stderr=subprocess.STDOUT, text=True))
+    for r, p in enumerate(procs):
+        try:
+            out, _ = p.communicate(timeout=300)
+        except subprocess.TimeoutExpired:
+            p.kill()
+            out, _ = p.communicate()
+        assert p.returncode == 0 and "RANK_OK" in out, f"rank {r}:\\n{out[-3000:]}"

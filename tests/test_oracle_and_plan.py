@@ -163,3 +163,54 @@ def test_plan_from_table_roundtrip():
     assert p.recs["page_id"].tolist() == [3, 4, 9]
     flat, begin = flatten_page_lists([[1, 2], [], [3]])
     assert flat.tolist() == [1, 2, 3] and begin.tolist() == [0, 2, 2, 3]
+
+
+def test_owner_split_covers_every_record_exactly_once(native):
+    """Union over owners of the owner-side plans == union of the workers' plans, and an
+    oracle gather run owner by owner fills the same worker tensors."""
+    from bikv_b200.push import split_plans_by_owner
+
+    g = KVGeometry(2, 2, 8, 4, torch.float16)
+    world, per = 3, 16
+    perm = np.random.default_rng(0).permutation(world * per * 4)
+    tables, nreq, tokens_of = [], [], []
+    for r in range(world):
+        rng = np.random.default_rng(10 + r)
+        tokens = rng.integers(1, 41, size=3)
+        counts = (tokens + 3) // 4
+        mine = perm[r * per * 4:(r + 1) * per * 4]
+        lists, at = [], 0
+        for c in counts:
+            lists.append(mine[at:at + int(c)].tolist())
+            at += int(c)
+        tables.append(build_plan(lists, tokens, 4, item_request=[0, 1, 2], n_requests=3).table.copy())
+        nreq.append(3)
+        tokens_of.append(tokens)
+
+    class _W:      # the two attributes the rest of the test reads
+        def __init__(self, t):
+            self.request_tokens, self.n_requests = t, len(t)
+    ws = [_W(t) for t in tokens_of]
+    shards = make_shards(g, world, per * 4, 2)
+    want = [make_workers(g, w.request_tokens) for w in ws]
+    for r in range(world):
+        O.gather(shards, g, [tuple(x) for x in tables[r].tolist()], want[r])
+    got = [make_workers(g, w.request_tokens) for w in ws]
+    flat = [t for ts in got for t in ts]
+    seen = 0
+    for owner in range(world):
+        push = split_plans_by_owner(tables, nreq, owner, world, per * 4)
+        assert ((push[:, 0] % world) == owner).all()
+        seen += len(push)
+        O.gather(shards, g, [tuple(x) for x in push.tolist()], flat)
+    assert seen == sum(len(t) for t in tables)
+    for a, b in zip(flat, [t for ts in want for t in ts]):
+        assert equal_bits(a, b)
+
+
+def test_table_views_outlive_their_plan(native):
+    """Pinned plan buffers are recycled, but never while a view of one is still around."""
+    a = build_plan([[1, 2, 3]], [40], 16).table          # the Plan itself is dropped at once
+    b = build_plan([[7, 8, 9]], [48], 16).table
+    assert a.tolist() == [[1, 16, 0, 0], [2, 16, 0, 16], [3, 8, 0, 32]]
+    assert b.tolist() == [[7, 16, 0, 0], [8, 16, 0, 16], [9, 16, 0, 32]]

@@ -68,6 +68,7 @@ def parse_args():
     ap.add_argument("--tune", action="append", default=[], metavar="KNOB=VALUE")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-verify", action="store_true", help="skip the pool checksum before and after the run")
     return ap.parse_args()
 
 
@@ -307,6 +308,8 @@ def run_config3(ctx):
             phase_end()
 
     sampler = ClockSampler(ctx["local_rank"]) if rank == 0 else None
+    torch.cuda.synchronize()
+    torch.cuda.empty_cache()      # scratch left by the pool fill; see main()
     for _ in range(args.warmup):
         step()
     torch.cuda.synchronize()
@@ -675,7 +678,12 @@ def main():
             total += words[at:at + step].sum(dtype=torch.int64)
         return int(total)
 
-    checksum_before = shard_checksum() if args.only == "both" else None
+    checksum_before = shard_checksum() if args.only == "both" and not args.no_verify else None
+    # Give back the scratch blocks that filling and checksumming the pool left in torch's
+    # caching allocator: with them still mapped the copy kernels measured 2 % slower
+    # (0.970 against 0.988 of the HBM copy peak, same box, back to back).
+    torch.cuda.synchronize()
+    torch.cuda.empty_cache()
     sampler = ClockSampler(local_rank) if rank == 0 else None
     for _ in range(args.warmup):
         step_resident()

@@ -7,6 +7,7 @@ host-resident plan is uploaded to.
 from __future__ import annotations
 
 import ctypes as C
+import threading
 from typing import Optional, Sequence, Union
 
 import numpy as np
@@ -28,7 +29,12 @@ class PageMover:
         self.device = torch.device(device if device is not None else f"cuda:{torch.cuda.current_device()}")
         self.variant = variant
         self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
-        self._scratch = torch.empty(1 << 20, dtype=torch.uint8, device=self.device)
+        # Plan staging on the device, one buffer per stream: calls on one stream reuse it in
+        # stream order; calls on different streams must not share it.
+        self._scratch_by_stream: dict = {}
+        # The reference serves its data methods from a 20-thread gRPC pool; one lock keeps
+        # this object's host-side state (staging buffers, tables, in-flight list) consistent.
+        self._lock = threading.RLock()
         self._req_ring: list = []     # [pinned table, event of the upload that read it]
         self._req_next = 0
         self._req_slot = 0
@@ -40,11 +46,18 @@ class PageMover:
         s = stream if stream is not None else torch.cuda.current_stream(self.device)
         return int(s.cuda_stream)
 
-    def _scratch_for(self, n_pages: int, n_requests: int) -> torch.Tensor:
+    def _scratch_for(self, n_pages: int, n_requests: int, stream=None) -> torch.Tensor:
         need = N.lib().bikv_plan_scratch_bytes(n_pages, n_requests)
-        if self._scratch.numel() < need:
-            self._scratch = torch.empty(int(need * 1.5), dtype=torch.uint8, device=self.device)
-        return self._scratch
+        key = self._stream(stream)
+        buf = self._scratch_by_stream.get(key)
+        if buf is None or buf.numel() < need:
+            # A buffer being replaced may still be read by queued work; torch frees it in
+            # stream order of ITS allocation stream, so wait for this stream first.
+            if buf is not None:
+                torch.cuda.current_stream(self.device).synchronize() if stream is None else stream.synchronize()
+            buf = torch.empty(max(int(need * 1.5), 1 << 20), dtype=torch.uint8, device=self.device)
+            self._scratch_by_stream[key] = buf
+        return buf
 
     def request_table(self, geom: KVGeometry, tensors: Tensors) -> torch.Tensor:
         """Host (pinned) int64 [n, 2] table of (base pointer, tokens) for worker tensors
@@ -81,10 +94,14 @@ class PageMover:
                variant: Optional[int], stream) -> None:
         if plan.n_pages == 0:
             return
+        with self._lock:
+            self._run_h_locked(fn, pool, plan, tensors, validate, variant, stream)
+
+    def _run_h_locked(self, fn, pool, plan, tensors, validate, variant, stream) -> None:
         reqs = self.request_table(pool.geom, tensors)
         if len(reqs) < plan.n_requests:
             raise ValueError(f"plan names {plan.n_requests} worker tensors, {len(reqs)} given")
-        scratch = self._scratch_for(plan.n_pages, len(reqs))
+        scratch = self._scratch_for(plan.n_pages, len(reqs), stream)
         g = pool.geom.native()
         rc = fn(C.byref(pool.desc), C.byref(g), C.c_void_p(plan.host_ptr), plan.n_pages,
                 C.c_void_p(reqs.data_ptr()), len(reqs), C.c_void_p(scratch.data_ptr()),
@@ -129,11 +146,15 @@ class PageMover:
     def _run_table(self, fn, pool, plan, request_table, validate, variant, stream) -> None:
         if plan.n_pages == 0:
             return
+        with self._lock:
+            self._run_table_locked(fn, pool, plan, request_table, validate, variant, stream)
+
+    def _run_table_locked(self, fn, pool, plan, request_table, validate, variant, stream) -> None:
         if request_table.dtype != torch.int64 or request_table.dim() != 2 or request_table.shape[1] != 2 \
                 or not request_table.is_contiguous() or request_table.is_cuda:
             raise ValueError("request_table must be a contiguous host int64 [n, 2] tensor")
         n = request_table.shape[0]
-        scratch = self._scratch_for(plan.n_pages, n)
+        scratch = self._scratch_for(plan.n_pages, n, stream)
         g = pool.geom.native()
         rc = fn(C.byref(pool.desc), C.byref(g), C.c_void_p(plan.host_ptr), plan.n_pages,
                 C.c_void_p(request_table.data_ptr()), n, C.c_void_p(scratch.data_ptr()), scratch.numel(),
@@ -192,13 +213,17 @@ class PageMover:
     def _run_nhd(self, fn, pool: ShardedPool, plan: Plan, layers, validate: bool, check_overlap: bool, stream) -> None:
         if plan.n_pages == 0:
             return
+        with self._lock:
+            self._run_nhd_locked(fn, pool, plan, layers, validate, check_overlap, stream)
+
+    def _run_nhd_locked(self, fn, pool, plan, layers, validate, check_overlap, stream) -> None:
         table, slots, _ = self.layer_table(pool.geom, layers)
         g = pool.geom.native()
         if validate:
             N.check(N.lib().bikv_plan_validate_nhd(C.c_void_p(plan.host_ptr), plan.n_pages, slots, C.byref(pool.desc),
                                                    C.byref(g), int(check_overlap)), "bikv_plan_validate_nhd")
         nbytes = plan.n_pages * 16
-        scratch = self._scratch_for(plan.n_pages, 0)
+        scratch = self._scratch_for(plan.n_pages, 0, stream)
         st = stream if stream is not None else torch.cuda.current_stream(self.device)
         with torch.cuda.stream(st):
             scratch[:nbytes].copy_(plan._store.view(torch.uint8).view(-1)[:nbytes], non_blocking=True)

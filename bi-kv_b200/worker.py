@@ -50,6 +50,11 @@ class Worker:
         self.cache_miss_dict: Dict = {}
         self.pool: Optional[ShardedPool] = None
         self.mover = PageMover(self.device)
+        # The model-side paged KV cache (``local_kvcache`` of Worker/Worker.py:68-78): one
+        # [blocks * block_size, 2, heads, dim] tensor per layer; allocated on demand.
+        self.local_kv_cache_block_size = page_size
+        self.local_max_kv_cache_blocks = 0
+        self.local_kvcache = []
 
     # -- wiring --------------------------------------------------------------
     def attach_pool(self, pool: ShardedPool) -> None:
@@ -93,6 +98,43 @@ class Worker:
         with torch.cuda.device(self.device):
             self.mover.scatter(self.pool, plan, self.compute_buffer)
         return plan.total_tokens
+
+    def init_local_kvcache(self, max_blocks: int) -> None:
+        """Allocates the paged per-layer KV cache with blocks of ``page_size`` tokens (the
+        reference uses 10240 blocks of 16 tokens, ``Worker.py:65-66``)."""
+        g = self.geometry
+        self.local_max_kv_cache_blocks = max_blocks
+        self.local_kvcache = [torch.zeros(max_blocks * self.page_size, 2, g.n_kv_heads, g.head_dim, dtype=g.dtype,
+                                          device=self.device) for _ in range(g.n_layers)]
+
+    def _block_plan(self, task, block_ids):
+        from .plan import build_block_plan
+
+        if self.pool is None or not self.local_kvcache:
+            raise RuntimeError(f"worker rank {self.rank}: pool and local_kvcache must be set up first")
+        if isinstance(task, dict):
+            pages, tokens, cw = task["cache_pages_list"], [p[1] for p in task["id_token_pair"]], task["cache_worker"]
+        else:
+            pages, tokens, cw = task.cache_pages_list, [p.token_num for p in task.id_token_pair], task.cache_worker
+        pages = [getattr(p, "cache_pages_list", p) for p in pages]
+        block = self.pool.rule == N.SHARD_BLOCK
+        return build_block_plan(pages, tokens, self.page_size, block_ids,
+                                item_shard=[cw] * len(tokens) if block else None,
+                                pages_per_shard=self.pool.pages_per_shard)
+
+    def pull_pages_to_blocks(self, combined_task_info, block_ids) -> None:
+        """Gather the task's pages straight into ``local_kvcache``: the k-th page of the task
+        (items in order) fills block ``block_ids[k]`` of every layer -- no intermediate tensor
+        between the pool and the cache the model's paged prefill reads."""
+        plan = self._block_plan(combined_task_info, block_ids)
+        with torch.cuda.device(self.device):
+            self.mover.gather_nhd(self.pool, plan, self.local_kvcache)
+
+    def push_pages_from_blocks(self, combined_task_info, block_ids) -> None:
+        """Scatter blocks of ``local_kvcache`` into the task's pool pages."""
+        plan = self._block_plan(combined_task_info, block_ids)
+        with torch.cuda.device(self.device):
+            self.mover.scatter_nhd(self.pool, plan, self.local_kvcache)
 
     def receive_kvcache_data_batch(self, combined_task_info):
         return self.pull_pages(combined_task_info)

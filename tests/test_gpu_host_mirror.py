@@ -198,3 +198,31 @@ def test_token_major_gather_equals_reference_kernel_plus_permute(cuda):
     B.PageMover(cuda).gather(B.ShardedPool.single(cache, g), plan, got)
     torch.cuda.synchronize()
     assert equal_bits(got, want)
+
+
+def test_worker_paged_cache_round_trip(cuda):
+    """Worker.local_kvcache filled straight from the pool and drained back into other pages."""
+    geom = KVGeometry(3, 2, 64, 16, torch.float16)
+    kvs = [KVCache(3 + 2 * i, 16 * 10, 16, 5000, {}, {}, None, geometry=geom, fill=0) for i in range(2)]
+    w = Worker(2, 5000, 64, 16, 1, {}, {}, None, geometry=geom)
+    Worker.connect(kvs, [w])
+    w.init_local_kvcache(12)
+    kvs[1].cuda_cache_data.copy_(normal(geom.pool_shape(10), geom.dtype, 9).to(cuda))
+    task = {"infer_worker": 0, "cache_worker": 1, "token_num": 40, "task_type": SIGNAL_SEND,
+            "id_token_pair": [(1, 24), (2, 16)], "cache_pages_list": [[4, 7], [2]]}
+    w.pull_pages_to_blocks(task, [9, 0, 5])
+    torch.cuda.synchronize()
+    pool1 = kvs[1].cuda_cache_data                                    # [10, L, 2, 16, H, D]
+    for l in range(geom.n_layers):
+        lay = w.local_kvcache[l]
+        assert equal_bits(lay[9 * 16:10 * 16], pool1[4, l].permute(1, 0, 2, 3))
+        assert equal_bits(lay[0:8], pool1[7, l, :, :8].permute(1, 0, 2, 3))       # 24 tokens: 16 + 8
+        assert int(lay[8:16].abs().sum()) == 0
+        assert equal_bits(lay[5 * 16:6 * 16], pool1[2, l].permute(1, 0, 2, 3))
+    back = {"infer_worker": 0, "cache_worker": 0, "token_num": 40, "task_type": SIGNAL_RECV,
+            "id_token_pair": [(1, 24), (2, 16)], "cache_pages_list": [[1, 3], [8]]}
+    w.push_pages_from_blocks(back, [9, 0, 5])
+    torch.cuda.synchronize()
+    pool0 = kvs[0].cuda_cache_data
+    assert equal_bits(pool0[1], pool1[4]) and equal_bits(pool0[8], pool1[2])
+    assert equal_bits(pool0[3][:, :, :8], pool1[7][:, :, :8]) and int(pool0[3][:, :, 8:].abs().sum()) == 0

@@ -153,6 +153,11 @@ def cpu_reference_run(steps, warmup, requests, budget_s=20.0):
     from bikv_b200 import workloads as W
     from oracle import bikv_oracle as O
 
+    # All the host cores this process may use (torchrun sets OMP_NUM_THREADS=1 for its ranks).
+    try:
+        torch.set_num_threads(len(os.sched_getaffinity(0)))
+    except (AttributeError, RuntimeError):
+        pass
     g = W.GEO_B
     pool_pages, sample_requests = 4096, min(8, requests)
     w = W.config1(seed=0, n_pages=pool_pages, n_requests=sample_requests)

@@ -68,6 +68,9 @@ def parse_args():
     ap.add_argument("--tune", action="append", default=[], metavar="KNOB=VALUE")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--host-kv-steps", type=int, default=2,
+                    help="N = 1: also time this many round trips with the worker KV tensors in pinned HOST memory "
+                         "(the reference keeps its worker buffer on the CPU); 0 skips it")
     ap.add_argument("--no-verify", action="store_true", help="skip the pool checksum before and after the run")
     return ap.parse_args()
 
@@ -197,6 +200,17 @@ def cpu_reference_run(steps, warmup, requests, budget_s=20.0):
 
 def run_reference_arm(args, rank):
     if rank != 0:
+        return
+    if os.environ.get("OMP_NUM_THREADS") and os.environ.get("BIKV_REFERENCE_CHILD") != "1":
+        # A launcher (torchrun) pinned this rank to OMP_NUM_THREADS threads, and the OpenMP
+        # pool cannot be widened after the fact: run the CPU arm in a child that starts with
+        # all host cores and pass its JSON line through.
+        env = {k: v for k, v in os.environ.items()
+               if k not in ("OMP_NUM_THREADS", "MKL_NUM_THREADS", "RANK", "LOCAL_RANK", "WORLD_SIZE")}
+        env["BIKV_REFERENCE_CHILD"] = "1"
+        res = subprocess.run([sys.executable, os.path.abspath(__file__)] + sys.argv[1:], env=env)
+        if res.returncode != 0:
+            raise SystemExit(res.returncode)
         return
     base = cpu_reference_run(args.steps, args.warmup, args.requests, budget_s=120.0)
     line = {
@@ -729,6 +743,7 @@ def main():
     mover.check_status()
 
     # ---- end to end through the Python API, host-resident plan ----
+    h2d_plan_bytes = 2 * (plan.n_pages * 16 + w.n_requests * 16)
     e2e = None
     if not args.no_e2e:
         for _ in range(max(1, min(args.warmup, 3))):
@@ -741,10 +756,42 @@ def main():
         torch.cuda.synchronize()
         e2e_s = time.perf_counter() - t0
         barrier()
-        h2d = 2 * (plan.n_pages * 16 + w.n_requests * 16)
-        e2e = {"seconds": e2e_s, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 16}
+        e2e = {"seconds": e2e_s, "h2d_bytes_per_step": h2d_plan_bytes, "d2h_bytes_per_step": 16}
 
     clocks = sampler.finish() if sampler else None
+
+    # ---- variant: worker KV in pinned host memory, written and read in place over PCIe ----
+    host_kv = None
+    if not multi and not nhd and args.host_kv_steps > 0 and not args.no_e2e and args.only == "both":
+        host = [torch.empty(geom.worker_shape(int(t)), dtype=geom.dtype).pin_memory() for t in w.request_tokens]
+        table = torch.empty((len(host), 2), dtype=torch.int64).pin_memory()
+        for i, t in enumerate(host):
+            table[i, 0], table[i, 1] = t.data_ptr(), t.shape[2]
+
+        def step_host_kv():
+            p = build_plan(flat_begin, item_tokens, geom.page_tokens, item_request=item_req, n_requests=w.n_requests,
+                           transient=True)
+            mover.gather_table(pool, p, table, variant=N.VARIANT_LDST)
+            mover.scatter_table(pool, p, table, variant=N.VARIANT_LDST)
+            mover.check_status()
+
+        step_host_kv()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(args.host_kv_steps):
+            step_host_kv()
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        same = all(torch.equal(a.view(torch.int16), b.cpu().view(torch.int16)) for a, b in
+                   list(zip(host, tensors))[:4]) if geom.elt_bytes == 2 else None
+        host_kv = {"value": 2 * w.payload_bytes * args.host_kv_steps / dt / 1e9, "unit": UNIT,
+                   "steps": args.host_kv_steps, "ms_per_step": dt / args.host_kv_steps * 1e3,
+                   "d2h_bytes_per_step": w.payload_bytes, "h2d_bytes_per_step": w.payload_bytes + h2d_plan_bytes,
+                   "host_tensors_equal_device_tensors": same,
+                   "what": "same round trip with the worker KV tensors in pinned host memory: the gather kernel "
+                           "stores into them and the scatter kernel loads from them in place over PCIe "
+                           "(the reference keeps its worker buffer on the CPU, Worker/Worker.py:57-62)"}
+        del host
 
     verified = None
     if checksum_before is not None:
@@ -820,6 +867,8 @@ def main():
                            "ms_per_step": e2e["seconds"] / args.steps * 1e3,
                            "what": "build_plan from page lists + PageMover.gather + PageMover.scatter + status read, "
                                    "plan in pinned host memory; the pool and the worker KV tensors stay in HBM"}
+        if host_kv:
+            line["e2e_host_kv"] = host_kv
         if not multi and not args.no_cpu_baseline:
             base = cpu_reference_run(20, 1, args.requests, budget_s=15.0)
             line["cpu_baseline"] = {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")}

@@ -88,3 +88,36 @@ def test_gather_against_torch_gpu_ops(cuda):
           f"{nbytes / t_torch / 1e6:.1f} GB/s ({t_torch:.3f} ms), bikv_gather {nbytes / t_new / 1e6:.1f} GB/s "
           f"({t_new:.3f} ms), x{t_torch / t_new:.2f}")
     assert t_new <= t_torch
+
+
+def test_zero_copy_from_pinned_host_against_reference_kernel(cuda):
+    """Source pages in pinned host memory: the reference's zero_copy_page_kernel
+    (copy_kernel.cu:39-66) against bikv_copy_pages_flat on the same pinned tensor -- same
+    bits; both are bound by the host link, the rates are printed."""
+    path = os.path.join(ROOT, "oracle", "_ref", "bikv_ref_kernel.so")
+    if not os.path.exists(path):
+        pytest.skip("oracle/_ref/bikv_ref_kernel.so not built")
+    spec = importlib.util.spec_from_file_location("bikv_ref_kernel", path)
+    ref = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(ref)
+    g = B.GEO_R
+    page_size, n_pages, pool_pages = 16, 512, 1024
+    elems = page_size * g.token_elems
+    pinned = torch.randn((pool_pages * page_size,) + g.token_shape, dtype=torch.float32).to(torch.float16).pin_memory()
+    rng = np.random.default_rng(2)
+    src = torch.from_numpy((rng.permutation(pool_pages)[:n_pages] * elems).astype(np.int64)).to(cuda)
+    dst = torch.from_numpy((rng.permutation(n_pages) * elems).astype(np.int64)).to(cuda)
+    out_ref = torch.zeros(n_pages * elems, dtype=torch.float16, device=cuda)
+    out_new = torch.zeros_like(out_ref)
+    mover = B.PageMover(cuda)
+    shape = ref.ref_zero_copy_pages(pinned, src, dst, out_ref, page_size, 128, 2, 28, 2)
+    assert list(shape) == [n_pages * page_size, 128, 2, 28, 2]
+    mover.copy_pages_flat(pinned, out_new, src, dst, elems)
+    torch.cuda.synchronize()
+    assert torch.equal(out_new.view(torch.int16), out_ref.view(torch.int16))
+    t_ref = _time(lambda: ref.ref_zero_copy_pages(pinned, src, dst, out_ref, page_size, 128, 2, 28, 2), iters=5)
+    t_new = _time(lambda: mover.copy_pages_flat(pinned, out_new, src, dst, elems), iters=5)
+    nbytes = n_pages * elems * 2
+    print(f"\n[zero-copy {n_pages} pages x {page_size} tokens = {nbytes / 2**20:.0f} MiB from pinned host memory] "
+          f"reference kernel {nbytes / t_ref / 1e6:.1f} GB/s, bikv_copy_pages_flat {nbytes / t_new / 1e6:.1f} GB/s")
+    assert t_new <= t_ref * 1.10

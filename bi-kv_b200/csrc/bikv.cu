@@ -22,6 +22,8 @@ std::atomic<long long> g_bulk_ctas_per_sm{3};
 std::atomic<long long> g_bulk_stages{4};
 std::atomic<long long> g_seg_bytes{16384};
 std::atomic<long long> g_auto_variant{0};  // 0 = choose by shard count
+std::atomic<long long> g_tm_threads{128};      // CTA size of k_token_major16v (128 measured best: 0.85 vs 0.82)
+std::atomic<long long> g_tm_max_groups{16};    // cap on d-groups per slab (k_token_major16v)
 
 int cuda_fail(cudaError_t e) {
   tl_cuda_error = (int)e;
@@ -185,7 +187,7 @@ int launch_token_major16v(const bikv_pool_desc* pool, const bikv_geometry* g, co
   while ((1u << ru_log2) < LU) ++ru_log2;
   const long long per_group = 8ll * H * (16ll << ru_log2);   // tile bytes per d-group
   unsigned Gs = 0;
-  for (unsigned cand = G; cand >= 1; --cand) {
+  for (unsigned cand = std::min<unsigned>(G, (unsigned)g_tm_max_groups.load()); cand >= 1; --cand) {
     if (G % cand) continue;
     if (per_group * cand <= 48 * 1024) {
       Gs = cand;
@@ -227,14 +229,14 @@ int launch_token_major16v(const bikv_pool_desc* pool, const bikv_geometry* g, co
   a.div_ptok = fast_div((unsigned)g->page_tokens);
   a.token_bytes = (unsigned long long)D * H * L * 4ull;
   a.to_pool = to_pool;
-  const long long per_sm = std::max<long long>(1, std::min<long long>(6, (220 * 1024) / (smem + 1024)));
+  const long long per_sm = std::max<long long>(1, std::min<long long>(12, (220 * 1024) / (smem + 1024)));
   const unsigned grid = (unsigned)std::min<long long>(items, (long long)di.sm_count * per_sm);
   if (grid == 0) return BIKV_OK;
   BIKV_CUDA(cudaFuncSetAttribute(k_token_major16v, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)std::max<long long>(2 * tile, 48 * 1024)));
   BIKV_CUDA(cudaFuncSetAttribute(k_token_major16v, cudaFuncAttributePreferredSharedMemoryCarveout,
                                  cudaSharedmemCarveoutMaxShared));
-  k_token_major16v<<<grid, 256, (size_t)smem, st>>>(a);
+  k_token_major16v<<<grid, (unsigned)g_tm_threads.load(), (size_t)smem, st>>>(a);
   return after_launch();
 }
 
@@ -416,6 +418,8 @@ Knob* find_knob(const char* name) {
       {"bulk_stages", &g_bulk_stages, 2, kMaxStages},
       {"seg_bytes", &g_seg_bytes, 1024, 64 * 1024},
       {"auto_variant", &g_auto_variant, 0, BIKV_VARIANT_BULK},
+      {"tm_threads", &g_tm_threads, 64, 256},
+      {"tm_max_groups", &g_tm_max_groups, 1, 64},
   };
   if (!name) return nullptr;
   for (auto& k : knobs)

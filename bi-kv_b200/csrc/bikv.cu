@@ -23,6 +23,7 @@ std::atomic<long long> g_bulk_stages{4};
 std::atomic<long long> g_seg_bytes{16384};
 std::atomic<long long> g_auto_variant{0};  // 0 = choose by shard count
 std::atomic<long long> g_tm_threads{128};      // CTA size of k_token_major16v (128 measured best: 0.85 vs 0.82)
+std::atomic<long long> g_tm16_threads{256};    // CTA size of k_token_major16
 std::atomic<long long> g_tm_max_groups{16};    // cap on d-groups per slab (k_token_major16v)
 
 int cuda_fail(cudaError_t e) {
@@ -171,7 +172,7 @@ int launch_token_major16(const bikv_pool_desc* pool, const bikv_geometry* g, con
     BIKV_CUDA(cudaFuncSetAttribute(k_token_major16, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   BIKV_CUDA(cudaFuncSetAttribute(k_token_major16, cudaFuncAttributePreferredSharedMemoryCarveout,
                                  cudaSharedmemCarveoutMaxShared));
-  k_token_major16<<<grid, 256, (size_t)smem, st>>>(a);
+  k_token_major16<<<grid, (unsigned)g_tm16_threads.load(), (size_t)smem, st>>>(a);
   return after_launch();
 }
 
@@ -419,6 +420,7 @@ Knob* find_knob(const char* name) {
       {"seg_bytes", &g_seg_bytes, 1024, 64 * 1024},
       {"auto_variant", &g_auto_variant, 0, BIKV_VARIANT_BULK},
       {"tm_threads", &g_tm_threads, 64, 256},
+      {"tm16_threads", &g_tm16_threads, 64, 256},
       {"tm_max_groups", &g_tm_max_groups, 1, 64},
   };
   if (!name) return nullptr;

@@ -23,6 +23,7 @@ std::atomic<long long> g_bulk_stages{4};
 std::atomic<long long> g_seg_bytes{16384};
 std::atomic<long long> g_auto_variant{0};  // 0 = choose by shard count
 std::atomic<long long> g_tm_threads{128};      // CTA size of k_token_major16v (128 measured best: 0.85 vs 0.82)
+std::atomic<long long> g_ldst_threads{256};    // CTA size of k_paged_ldst / k_paged_nhd / k_flat
 std::atomic<long long> g_tm16_threads{256};    // CTA size of k_token_major16
 std::atomic<long long> g_tm_max_groups{16};    // cap on d-groups per slab (k_token_major16v)
 
@@ -342,7 +343,7 @@ int launch_paged(const bikv_pool_desc* pool, const bikv_geometry* g, const bikv_
   if (items == 0) return BIKV_OK;
 
   if (variant == BIKV_VARIANT_LDST) {
-    const int threads = 256, warps = threads / 32;
+    const int threads = (int)g_ldst_threads.load() / 32 * 32, warps = threads / 32;
     const long long want = (items + warps - 1) / warps;
     unsigned grid = (unsigned)std::min<long long>(want, (long long)di.sm_count * g_ldst_ctas_per_sm.load());
     k_paged_ldst<8><<<grid, threads, 0, st>>>(a);
@@ -419,6 +420,7 @@ Knob* find_knob(const char* name) {
       {"bulk_stages", &g_bulk_stages, 2, kMaxStages},
       {"seg_bytes", &g_seg_bytes, 1024, 64 * 1024},
       {"auto_variant", &g_auto_variant, 0, BIKV_VARIANT_BULK},
+      {"ldst_threads", &g_ldst_threads, 64, 256},
       {"tm_threads", &g_tm_threads, 64, 256},
       {"tm16_threads", &g_tm16_threads, 64, 256},
       {"tm_max_groups", &g_tm_max_groups, 1, 64},

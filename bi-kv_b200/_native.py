@@ -122,6 +122,7 @@ SIGNATURES = {
     ),
     "bikv_copy_pages_flat": (C.c_int, [_P, _P, _P, _P, C.c_int64, C.c_int64, C.c_int32, _P]),
     "bikv_copy_range": (C.c_int, [_P, _P, C.c_int64, _P]),
+    "bikv_selftest_wait_timeout": (C.c_int, [_P, C.c_int64, _P]),
     "bikv_can_access_peer": (C.c_int, [C.c_int, C.c_int, C.POINTER(C.c_int)]),
     "bikv_enable_peer": (C.c_int, [C.c_int, C.c_int]),
     "bikv_pool_export": (C.c_int, [_P, C.c_char_p, C.POINTER(C.c_int64)]),

@@ -688,6 +688,12 @@ int bikv_copy_pages_flat(const void* src, void* dst, const int64_t* src_off_dev,
   return after_launch();
 }
 
+int bikv_selftest_wait_timeout(int32_t* status_dev, int64_t limit_ns, void* stream) {
+  if (!status_dev || limit_ns <= 0 || limit_ns > 1000000000ll) return BIKV_ERR_BAD_ARG;
+  k_selftest_wait_timeout<<<1, 32, 0, (cudaStream_t)stream>>>(status_dev, (unsigned long long)limit_ns);
+  return after_launch();
+}
+
 int bikv_copy_range(void* dst, const void* src, int64_t bytes, void* stream) {
   if (bytes < 0) return BIKV_ERR_BAD_ARG;
   return bikv_copy_pages_flat(src, dst, nullptr, nullptr, 1, bytes, 1, stream);

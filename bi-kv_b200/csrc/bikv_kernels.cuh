@@ -268,10 +268,12 @@ __device__ __forceinline__ unsigned long long global_timer_ns() {
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
 }
-// Bounded wait: at most ~2 s of wall time and at most 2^24 polls.
-__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
+// Bounded wait: at most `limit_ns` of wall time (2 s in the copy ring) and at most
+// 2^24 polls.
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
+                                                  unsigned long long limit_ns = 2000000000ull) {
   if (mbar_try_wait(bar, parity)) return true;
-  const unsigned long long deadline = global_timer_ns() + 2000000000ull;
+  const unsigned long long deadline = global_timer_ns() + limit_ns;
   for (unsigned i = 0; i < (1u << 24); ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((i & 63) == 63 && global_timer_ns() > deadline) break;
@@ -362,6 +364,18 @@ __global__ void __launch_bounds__(32) k_paged_bulk(const __grid_constant__ Paged
     for (int s = 0; s < stages; ++s)
       if (loaded_bits & (1u << s)) (void)mbar_wait_bounded(smem_u32(&bars[s]), (phase_bits >> s) & 1);
   }
+}
+
+// Diagnostic: one thread waits, with a short limit, on an mbarrier whose transaction
+// count nothing will ever satisfy, and reports the expiry exactly as the copy ring
+// does.  Exercises the bounded wait and the status word without a fault or a hang.
+__global__ void k_selftest_wait_timeout(int* status, unsigned long long limit_ns) {
+  __shared__ __align__(8) unsigned long long bar;
+  if (threadIdx.x != 0) return;
+  mbar_init(smem_u32(&bar), 1);
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  mbar_expect_tx(smem_u32(&bar), 16);   // 16 bytes that no copy delivers
+  if (!mbar_wait_bounded(smem_u32(&bar), 0, limit_ns)) atomicExch(status, (int)BIKV_ERR_DEVICE_TIMEOUT);
 }
 
 // ---------------------------------------------------------------------------

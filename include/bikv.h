@@ -280,6 +280,15 @@ int bikv_copy_pages_flat(const void* src, void* dst, const int64_t* src_off_dev,
  */
 int bikv_copy_range(void* dst, const void* src, int64_t bytes, void* stream);
 
+/*
+ * Diagnostic with no counterpart in the reference: launches one thread that waits
+ * on a barrier nothing will complete, with a limit of limit_ns (at most 1 s), so
+ * that the wait runs out and status_dev[0] receives BIKV_ERR_DEVICE_TIMEOUT -- the
+ * path a copy ring takes when a bulk copy never arrives.  The kernel returns by
+ * itself; the context stays usable.
+ */
+int bikv_selftest_wait_timeout(int32_t* status_dev, int64_t limit_ns, void* stream);
+
 /* ---- peer mapping -------------------------------------------------------- */
 /* cudaDeviceCanAccessPeer / cudaDeviceEnablePeerAccess for in-process pools;
  * already-enabled is success. */

@@ -287,3 +287,24 @@ def test_size_limits_are_refused_not_truncated(native):
     big.n_shards, big.shard_rule, big.pages_per_shard = 2, N.SHARD_MOD, 1 << 31
     assert native.bikv_gather(C.byref(big), C.byref(g), C.c_void_p(0x1000), 1, C.c_void_p(0x2000), 1,
                               N.VARIANT_LDST, None, None) == N.ERR_TOO_LARGE
+
+
+def test_bounded_device_wait_reports_a_timeout_and_the_context_survives(cuda):
+    """A wait that nothing satisfies runs out after its limit, the status word carries
+    BIKV_ERR_DEVICE_TIMEOUT, check_status raises and clears it, and the GPU keeps working."""
+    import ctypes as C
+    import time
+    mover = B.PageMover(cuda)
+    stream = C.c_void_p(torch.cuda.current_stream(cuda).cuda_stream)
+    t0 = time.perf_counter()
+    N.check(N.lib().bikv_selftest_wait_timeout(C.c_void_p(mover.status.data_ptr()), 20_000_000, stream))
+    torch.cuda.synchronize()
+    waited = time.perf_counter() - t0
+    assert 0.015 < waited < 1.0, waited
+    with pytest.raises(B.BikvError) as e:
+        mover.check_status()
+    assert e.value.status == N.ERR_DEVICE_TIMEOUT
+    mover.check_status()                                    # cleared
+    run_case(cuda, SMALL, 1, 8, 2, 40, N.VARIANT_BULK, seed=3)     # the context is still usable
+    assert N.lib().bikv_selftest_wait_timeout(None, 1000, None) == N.ERR_BAD_ARG
+    assert N.lib().bikv_selftest_wait_timeout(C.c_void_p(mover.status.data_ptr()), 2_000_000_000, None) == N.ERR_BAD_ARG

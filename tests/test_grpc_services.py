@@ -106,3 +106,89 @@ def test_transfers_driven_through_grpc(cuda):
     finally:
         kserver.stop(0)
         wserver.stop(0)
+
+
+def _free_base(ranks):
+    """A master_port such that master_port + rank is free for every rank (the reference's
+    port convention, rpc_def.py:50-57)."""
+    import random
+    import socket
+    rnd = random.Random()
+    for _ in range(200):
+        base = rnd.randrange(20000, 50000)
+        socks = []
+        try:
+            for r in ranks:
+                s = socket.socket()
+                s.bind(("127.0.0.1", base + r))
+                socks.append(s)
+            return base
+        except OSError:
+            continue
+        finally:
+            for s in socks:
+                s.close()
+    raise RuntimeError("no free port range")
+
+
+@pytest.mark.gpu
+def test_full_chain_coordinator_shards_worker_over_grpc(cuda):
+    """Coordinator (rank 1), worker (rank 2) and two shards (ranks 3, 5) as gRPC servers on
+    the reference's ports; a client plays the worker's request loop: RECV (write back), then
+    CHECK (hit -> SEND).  Data must come back bit for bit."""
+    import torch
+
+    from bikv_b200 import _native as N
+    from bikv_b200.cache_coordinator import CacheCoordinator
+    from bikv_b200.geometry import KVGeometry
+    from bikv_b200.kvcache import KVCache
+    from bikv_b200.worker import Worker
+    from helpers import equal_bits, normal
+
+    geom = KVGeometry(2, 2, 64, 16, torch.float16)
+    base = _free_base([1, 2, 3, 5])
+    ips = {r: "127.0.0.1" for r in (1, 2, 3, 5)}
+    servers = []
+
+    def serve(rank, register):
+        s = grpc.server(futures.ThreadPoolExecutor(max_workers=4))
+        register(s)
+        assert s.add_insecure_port(f"127.0.0.1:{base + rank}") == base + rank
+        s.start()
+        servers.append(s)
+
+    worker = Worker(2, base, 128, 16, 1, ips, {}, None, geometry=geom)
+    kvs = [KVCache(3 + 2 * i, 16 * 16, 16, base, ips, {}, None, geometry=geom, fill=0) for i in range(2)]
+    from bikv_b200.pool import ShardedPool
+    worker.attach_pool(ShardedPool.from_tensors([k.cuda_cache_data for k in kvs], geom, rule=N.SHARD_BLOCK))
+    for k in kvs:
+        k.stub_factory = G.worker_stub_factory()
+    cc = CacheCoordinator(1, base, [0, 1], [0], 16 * 16, 16, ips, None, policy="lru")
+    serve(2, lambda s: G.add_InferWorkerServiceServicer_to_server(worker, s))
+    for i, k in enumerate(kvs):
+        serve(3 + 2 * i, lambda s, k=k: G.add_KVCacheServiceServicer_to_server(k, s))
+    serve(1, lambda s: G.add_CacheCoordinatorServiceServicer_to_server(cc, s))
+    try:
+        with grpc.insecure_channel(f"127.0.0.1:{base + 1}") as ch:
+            stub = G.CacheCoordinatorServiceStub(ch)
+            stub.StartProcessRequest(pb.StartRequest(msg="go"), timeout=10)
+            data = normal(geom.worker_shape(50), geom.dtype, 7)
+            worker.compute_buffer[:, :, :50] = data.to(cuda)
+            recv = pb.TaskInfoList(tasks=[pb.TaskInfo(request_id=1, id=42, infer_worker=0, token_num=50,
+                                                      task_type=SIGNAL_RECV, task_num=1, type="item cache")])
+            stub.ReceiveTasksFromInferWorker(recv, timeout=10)
+            stub.PollBatchFromInferWorker(recv, timeout=60)
+            torch.cuda.synchronize()
+            worker.compute_buffer.zero_()
+            check = pb.TaskInfoList(tasks=[pb.TaskInfo(request_id=2, id=42, infer_worker=0, token_num=50,
+                                                       task_type=4, task_num=1, type="item cache")])
+            stub.ReceiveTasksFromInferWorker(check, timeout=10)
+            reply = stub.PollBatchFromInferWorker(check, timeout=60)
+            assert json.loads(reply.msg) == {"2": {"42": 1}}
+        torch.cuda.synchronize()
+        assert equal_bits(worker.compute_buffer[:, :, :50], data)
+        assert sum(k.recv_counter for k in kvs) == 1 and sum(k.send_counter for k in kvs) == 1
+    finally:
+        cc.stop()
+        for s in servers:
+            s.stop(0)

@@ -89,6 +89,29 @@ class CacheCoordinator:
             self._gc_timer.daemon = True
             self._gc_timer.start()
 
+    def read_prepared_data(self, data_path: str, index_path: str) -> int:
+        """Pre-warms the page table from two JSON files, as the Go coordinator does at start-up
+        when configured (``PageManager.go:536-563``): ``data_path`` maps item id (as a string)
+        to its token count, ``index_path`` lists ids hottest first; ids from a file whose name
+        contains "user" are looked up at ``id + 2000000``.  Items are loaded with weight 0
+        until the pages handed out exceed the whole pool.  Returns the number loaded."""
+        with open(data_path) as f:
+            data = json.load(f)
+        with open(index_path) as f:
+            ids = json.load(f)
+        user_file = "user" in index_path
+        limit = self.kvcache_num * self.page_manager.num_pages
+        total = loaded = 0
+        with self._lock:
+            for k in ids:
+                tokens = int(data.get(str(k + 2000000 if user_file else k), 0))
+                self.page_manager.load_item(int(k), tokens, 0, "prepared")
+                loaded += 1
+                total += (tokens + self.page_manager.page_size - 1) // self.page_manager.page_size
+                if total > limit:
+                    break
+        return loaded
+
     # -- service methods ------------------------------------------------------
     def ReceiveTasksFromInferWorker(self, request, context):
         with self._wake:

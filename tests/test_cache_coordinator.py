@@ -121,3 +121,24 @@ def test_over_grpc_with_the_loop_thread():
         cc.stop()
         cserver.stop(0)
         sserver.stop(0)
+
+
+def test_prewarm_from_json(tmp_path):
+    cc, _ = make(n_shards=2)
+    data = {str(i): 16 * (1 + i % 5) for i in range(100)}
+    (tmp_path / "item_len.json").write_text(json.dumps(data))
+    (tmp_path / "item_hot.json").write_text(json.dumps(list(range(100))))
+    n = cc.read_prepared_data(str(tmp_path / "item_len.json"), str(tmp_path / "item_hot.json"))
+    assert 0 < n <= 100
+    assert cc.page_manager.access_item(0)[0] is not None           # the hottest item is resident
+    q = pb.TaskInfoList(tasks=[task(1, 0, SIGNAL_CHECK), task(1, 1, SIGNAL_CHECK)])
+    cc.ReceiveTasksFromInferWorker(q, None)
+    cc.process_pending()
+    assert cc.cache_miss_dict[1] == {0: CACHE_HIT, 1: CACHE_HIT}
+    # ids of a "user" index are looked up at id + 2000000
+    udata = {str(2000000 + i): 32 for i in range(5)}
+    (tmp_path / "user_len.json").write_text(json.dumps(udata))
+    (tmp_path / "user_hot.json").write_text(json.dumps([0, 1, 2, 3, 4]))
+    cc2, _ = make(n_shards=1)
+    assert cc2.read_prepared_data(str(tmp_path / "user_len.json"), str(tmp_path / "user_hot.json")) == 5
+    assert len(cc2.page_manager.access_item(3)[1]) == 2

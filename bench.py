@@ -47,6 +47,8 @@ def parse_args():
                     help="auto = configuration 1 (N = 1) or 2 (N > 1), the benchmark; config3 = long-context "
                          "geometry, requests streamed; config4 = coordinator-driven prefix reuse, N/2 shard GPUs + "
                          "N/2 worker GPUs (both are additional measurements)")
+    ap.add_argument("--c3-order", default="longest", choices=["longest", "arrival"],
+                    help="config3: stream each rank's requests longest first (balances the ranks' phases) or in arrival order")
     ap.add_argument("--c4-requests", type=int, default=20000)
     ap.add_argument("--c4-planner", default="native", choices=["native", "python"],
                     help="config4: page directory in C++ (bikv_pm_*) or the Python page managers (order='fast')")
@@ -301,7 +303,8 @@ def run_config3(ctx):
     # Longest first on every rank: phase k then moves every rank's k-th longest request, so
     # the ranks' phases are close in size (max/mean 1.08 instead of 1.23 in arrival order) and
     # the barrier after each phase waits less.
-    reqs.sort(key=lambda x: -x.total_tokens)
+    if args.c3_order == "longest":
+        reqs.sort(key=lambda x: -x.total_tokens)
     arena = torch.zeros(geom.token_elems * max(w.total_tokens for w in reqs), dtype=geom.dtype, device=dev)
     mover = B.PageMover(dev, variant=ctx["variant"])
     staged = []
@@ -375,7 +378,7 @@ def run_config3(ctx):
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": elapsed_ms / args.steps,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u16", "data": "synthetic",
             "config": {"workload": f"config3: Llama-3-70B-like KV (80 layers, 8 KV heads, head 128, fp16, 16-token pages), "
-                                   f"{args.requests} requests per GPU of U[16k,32k] tokens streamed one at a time, longest first, pool "
+                                   f"{args.requests} requests per GPU of U[16k,32k] tokens streamed one at a time ({args.c3_order} order), pool "
                                    f"{args.pool_pages} pages per GPU striped page_id mod {world} [ADDITIONAL MEASUREMENT]",
                        "payload_bytes_per_direction_per_gpu": payload, "page_bytes": geom.page_bytes,
                        "l2": "inputs larger than L2 (each request is 5-10 GB)"},

@@ -113,8 +113,8 @@ SIGNATURES = {
         [C.POINTER(PoolDesc), C.POINTER(Geometry), _P, C.c_int64, _P, C.c_int32, _P, C.c_int64,
          C.c_int, C.c_int, _P, _P],
     ),
-    "bikv_gather_nhd": (C.c_int, [C.POINTER(PoolDesc), C.POINTER(Geometry), _P, C.c_int64, _P, C.c_int64, _P]),
-    "bikv_scatter_nhd": (C.c_int, [C.POINTER(PoolDesc), C.POINTER(Geometry), _P, C.c_int64, _P, C.c_int64, _P]),
+    "bikv_gather_nhd": (C.c_int, [C.POINTER(PoolDesc), C.POINTER(Geometry), _P, C.c_int64, _P, C.c_int64, _P, _P]),
+    "bikv_scatter_nhd": (C.c_int, [C.POINTER(PoolDesc), C.POINTER(Geometry), _P, C.c_int64, _P, C.c_int64, _P, _P]),
     "bikv_plan_validate_nhd": (C.c_int, [_P, C.c_int64, C.c_int64, C.POINTER(PoolDesc), C.POINTER(Geometry), C.c_int]),
     "bikv_gather_h_static": (
         C.c_int,

@@ -118,7 +118,7 @@ FastDiv fast_div(unsigned d) {
 // Token-major pool with 2-byte elements and head_dim a multiple of 8.
 int launch_token_major16(const bikv_pool_desc* pool, const bikv_geometry* g, const bikv_page_rec* recs,
                          long long n_pages, const bikv_request_desc* reqs, int to_pool, cudaStream_t st,
-                         const DeviceInfo& di) {
+                         const DeviceInfo& di, int32_t* status, int32_t n_requests) {
   const unsigned H = g->n_kv_heads, D = g->head_dim, L = g->n_layers;
   const unsigned G = D / 8;
   const unsigned Lp = L | 1u;
@@ -156,6 +156,9 @@ int launch_token_major16(const bikv_pool_desc* pool, const bikv_geometry* g, con
   a.Lp = Lp;
   a.token_bytes = (unsigned long long)D * H * L * 4ull;
   a.to_pool = to_pool;
+  a.status = status;
+  a.n_requests = (unsigned)n_requests;
+  a.total_pages = (unsigned long long)pool->pages_per_shard * pool->n_shards;
   a.div_L = fast_div(L);
   a.div_H = fast_div(H);
   a.div_HG = fast_div(H * Gs);
@@ -182,7 +185,7 @@ int launch_token_major16(const bikv_pool_desc* pool, const bikv_geometry* g, con
 // Returns 1 if the geometry does not fit this kernel (caller falls back).
 int launch_token_major16v(const bikv_pool_desc* pool, const bikv_geometry* g, const bikv_page_rec* recs,
                           long long n_pages, const bikv_request_desc* reqs, int to_pool, cudaStream_t st,
-                          const DeviceInfo& di) {
+                          const DeviceInfo& di, int32_t* status, int32_t n_requests) {
   const unsigned H = g->n_kv_heads, D = g->head_dim, L = g->n_layers;
   const unsigned G = D / 8, LU = L / 4;
   unsigned ru_log2 = 3;
@@ -231,6 +234,9 @@ int launch_token_major16v(const bikv_pool_desc* pool, const bikv_geometry* g, co
   a.div_ptok = fast_div((unsigned)g->page_tokens);
   a.token_bytes = (unsigned long long)D * H * L * 4ull;
   a.to_pool = to_pool;
+  a.status = status;
+  a.n_requests = (unsigned)n_requests;
+  a.total_pages = (unsigned long long)pool->pages_per_shard * pool->n_shards;
   const long long per_sm = std::max<long long>(1, std::min<long long>(12, (220 * 1024) / (smem + 1024)));
   const unsigned grid = (unsigned)std::min<long long>(items, (long long)di.sm_count * per_sm);
   if (grid == 0) return BIKV_OK;
@@ -244,16 +250,16 @@ int launch_token_major16v(const bikv_pool_desc* pool, const bikv_geometry* g, co
 
 int launch_token_major(const bikv_pool_desc* pool, const bikv_geometry* g, const bikv_page_rec* recs,
                        long long n_pages, const bikv_request_desc* reqs, int to_pool,
-                       cudaStream_t st) {
+                       cudaStream_t st, int32_t* status, int32_t n_requests) {
   DeviceInfo di;
   int rc = device_info(&di);
   if (rc) return rc;
   if (g->elt_bytes == 2 && g->head_dim % 8 == 0 && g->n_layers % 4 == 0) {
-    rc = launch_token_major16v(pool, g, recs, n_pages, reqs, to_pool, st, di);
+    rc = launch_token_major16v(pool, g, recs, n_pages, reqs, to_pool, st, di, status, n_requests);
     if (rc != 1) return rc;
   }
   if (g->elt_bytes == 2 && g->head_dim % 8 == 0)
-    return launch_token_major16(pool, g, recs, n_pages, reqs, to_pool, st, di);
+    return launch_token_major16(pool, g, recs, n_pages, reqs, to_pool, st, di, status, n_requests);
   const unsigned V = 16 / g->elt_bytes;
   const unsigned C = 2u * g->n_layers;
   const unsigned H = g->n_kv_heads, D = g->head_dim;
@@ -290,6 +296,9 @@ int launch_token_major(const bikv_pool_desc* pool, const bikv_geometry* g, const
   a.C = C;
   a.token_bytes = (unsigned long long)per_d * D;
   a.to_pool = to_pool;
+  a.status = status;
+  a.n_requests = (unsigned)n_requests;
+  a.total_pages = (unsigned long long)pool->pages_per_shard * pool->n_shards;
   const int threads = 256;
   int per_sm = (int)std::max<long long>(1, std::min<long long>(8, (200 * 1024) / std::max<long long>(smem, 1)));
   unsigned grid = (unsigned)std::min<long long>(items, (long long)di.sm_count * per_sm);
@@ -309,7 +318,7 @@ int launch_token_major(const bikv_pool_desc* pool, const bikv_geometry* g, const
 
 int launch_paged(const bikv_pool_desc* pool, const bikv_geometry* g, const bikv_page_rec* recs,
                  long long n_pages, const bikv_request_desc* reqs, int to_pool, int variant,
-                 int32_t* status, cudaStream_t st) {
+                 int32_t* status, cudaStream_t st, int32_t n_requests) {
   DeviceInfo di;
   int rc = device_info(&di);
   if (rc) return rc;
@@ -340,6 +349,9 @@ int launch_paged(const bikv_pool_desc* pool, const bikv_geometry* g, const bikv_
   a.n_items = (unsigned)items;
   a.to_pool = to_pool;
   a.status = status;
+  a.n_requests = (unsigned)n_requests;
+  a.page_tokens = (unsigned)g->page_tokens;
+  a.total_pages = (unsigned long long)pool->pages_per_shard * pool->n_shards;
   if (items == 0) return BIKV_OK;
 
   if (variant == BIKV_VARIANT_LDST) {
@@ -377,8 +389,8 @@ int run(const bikv_pool_desc* pool, const bikv_geometry* geom, const bikv_page_r
   if (!recs_dev || !reqs_dev || n_requests == 0) return BIKV_ERR_BAD_ARG;
   cudaStream_t st = (cudaStream_t)stream;
   if (geom->pool_layout == BIKV_POOL_TOKEN_MAJOR)
-    return launch_token_major(pool, geom, recs_dev, n_pages, reqs_dev, to_pool, st);
-  return launch_paged(pool, geom, recs_dev, n_pages, reqs_dev, to_pool, variant, status_dev, st);
+    return launch_token_major(pool, geom, recs_dev, n_pages, reqs_dev, to_pool, st, status_dev, n_requests);
+  return launch_paged(pool, geom, recs_dev, n_pages, reqs_dev, to_pool, variant, status_dev, st, n_requests);
 }
 
 int run_h(const bikv_pool_desc* pool, const bikv_geometry* geom, const bikv_page_rec* recs_host,
@@ -565,7 +577,7 @@ int bikv_plan_validate(const bikv_page_rec* recs, int64_t n_pages, const bikv_re
 
 static int run_nhd(const bikv_pool_desc* pool, const bikv_geometry* geom, const bikv_page_rec* recs_dev,
                    int64_t n_pages, void* const* layer_bases_dev, int64_t slots_per_layer, int to_pool,
-                   void* stream) {
+                   int32_t* status_dev, void* stream) {
   int rc = check_geometry(geom);
   if (rc) return rc;
   rc = check_pool(pool);
@@ -591,6 +603,10 @@ static int run_nhd(const bikv_pool_desc* pool, const bikv_geometry* geom, const 
   if (items > 0x7fffffffll) return BIKV_ERR_TOO_LARGE;
   a.n_items = (unsigned)items;
   a.to_pool = to_pool;
+  a.status = status_dev;
+  a.page_tokens = (unsigned)geom->page_tokens;
+  a.total_pages = (unsigned long long)pool->pages_per_shard * pool->n_shards;
+  a.slots_per_layer = slots_per_layer;
   const int threads = 256, warps = threads / 32;
   const long long want = (items + warps - 1) / warps;
   const unsigned grid = (unsigned)std::min<long long>(want, (long long)di.sm_count * g_ldst_ctas_per_sm.load());
@@ -599,13 +615,15 @@ static int run_nhd(const bikv_pool_desc* pool, const bikv_geometry* geom, const 
 }
 
 int bikv_gather_nhd(const bikv_pool_desc* pool, const bikv_geometry* geom, const bikv_page_rec* recs_dev,
-                    int64_t n_pages, void* const* layer_bases_dev, int64_t slots_per_layer, void* stream) {
-  return run_nhd(pool, geom, recs_dev, n_pages, layer_bases_dev, slots_per_layer, 0, stream);
+                    int64_t n_pages, void* const* layer_bases_dev, int64_t slots_per_layer,
+                    int32_t* status_dev, void* stream) {
+  return run_nhd(pool, geom, recs_dev, n_pages, layer_bases_dev, slots_per_layer, 0, status_dev, stream);
 }
 
 int bikv_scatter_nhd(const bikv_pool_desc* pool, const bikv_geometry* geom, const bikv_page_rec* recs_dev,
-                     int64_t n_pages, void* const* layer_bases_dev, int64_t slots_per_layer, void* stream) {
-  return run_nhd(pool, geom, recs_dev, n_pages, layer_bases_dev, slots_per_layer, 1, stream);
+                     int64_t n_pages, void* const* layer_bases_dev, int64_t slots_per_layer,
+                     int32_t* status_dev, void* stream) {
+  return run_nhd(pool, geom, recs_dev, n_pages, layer_bases_dev, slots_per_layer, 1, status_dev, stream);
 }
 
 int bikv_plan_validate_nhd(const bikv_page_rec* recs, int64_t n_pages, int64_t slots_per_layer,

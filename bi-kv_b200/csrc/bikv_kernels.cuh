@@ -45,7 +45,34 @@ struct PagedArgs {
   unsigned long long page_bytes;   // planes * plane_bytes
   int to_pool;                     // 0 = gather (pool -> worker), 1 = scatter
   int* status;
+  unsigned n_requests;             // bounds for the record checks below
+  unsigned page_tokens;
+  unsigned long long total_pages;  // n_shards * pages_per_shard
 };
+
+// A record that points outside the pool or outside its worker tensor is skipped, never
+// dereferenced, and the first such error is left in the caller's status word (if one was
+// given): plans that reach the device entry points cannot be checked on the host.
+__device__ __forceinline__ bool record_ok(const uint4& r, unsigned n_requests, unsigned page_tokens,
+                                          unsigned long long total_pages, int* status) {
+  int err = 0;
+  if ((unsigned long long)r.x >= total_pages)
+    err = BIKV_ERR_PAGE_RANGE;
+  else if (r.y == 0 || r.y > page_tokens)
+    err = BIKV_ERR_PLAN;
+  else if (r.z >= n_requests)
+    err = BIKV_ERR_BAD_ARG;
+  else if ((int)r.w < 0)
+    err = BIKV_ERR_DST_RANGE;
+  if (err == 0) return true;
+  if (status) atomicCAS(status, 0, err);
+  return false;
+}
+__device__ __forceinline__ bool window_ok(const uint4& r, long long tensor_tokens, int* status) {
+  if ((long long)r.w + (long long)r.y <= tensor_tokens) return true;
+  if (status) atomicCAS(status, 0, (int)BIKV_ERR_DST_RANGE);
+  return false;
+}
 
 __device__ __forceinline__ uint4 ld_stream16(const void* p) {
   uint4 v;
@@ -69,6 +96,7 @@ __device__ __forceinline__ bool decode_item(const PagedArgs& a, unsigned w, char
   const unsigned plane = t % a.planes;
   const unsigned page = t / a.planes;
   const uint4 r = __ldg(a.recs + page);
+  if (!record_ok(r, a.n_requests, a.page_tokens, a.total_pages, a.status)) return false;
   const unsigned vbytes = r.y * a.row_bytes;
   const unsigned off = part * a.seg_bytes;
   if (off >= vbytes) return false;
@@ -85,6 +113,7 @@ __device__ __forceinline__ bool decode_item(const PagedArgs& a, unsigned w, char
   }
   pool_p = a.pool.base[shard] + local * a.page_bytes + (unsigned long long)plane * a.plane_bytes + off;
   const longlong2 rq = __ldg(reinterpret_cast<const longlong2*>(a.reqs + r.z));
+  if (!window_ok(r, rq.y, a.status)) return false;
   work_p = reinterpret_cast<char*>(rq.x) +
            ((unsigned long long)plane * (unsigned long long)rq.y + r.w) * a.row_bytes + off;
   return true;
@@ -179,6 +208,10 @@ struct NhdArgs {
   unsigned plane_bytes;
   unsigned long long page_bytes;
   int to_pool;
+  int* status;
+  unsigned page_tokens;
+  unsigned long long total_pages;
+  long long slots_per_layer;
 };
 
 template <int U>
@@ -189,7 +222,10 @@ __global__ void __launch_bounds__(256) k_paged_nhd(const __grid_constant__ NhdAr
   for (unsigned w = blockIdx.x * warps_per_cta + (threadIdx.x >> 5); w < a.n_items; w += stride) {
     const unsigned plane = w % a.planes;
     const unsigned page = w / a.planes;
-    const uint4 r = __ldg(a.recs + page);
+    uint4 r = __ldg(a.recs + page);
+    r.z = 0;  // the request field is unused for a paged worker cache
+    if (!record_ok(r, 1, a.page_tokens, a.total_pages, a.status) || !window_ok(r, a.slots_per_layer, a.status))
+      continue;
     const unsigned id = r.x;
     unsigned shard;
     unsigned long long local;
@@ -434,6 +470,9 @@ struct TokenMajorArgs {
   unsigned H, D, C;
   unsigned long long token_bytes;  // D*H*C*elt
   int to_pool;
+  int* status;
+  unsigned n_requests;
+  unsigned long long total_pages;
 };
 
 template <typename T>
@@ -452,7 +491,8 @@ __global__ void __launch_bounds__(256) k_token_major(const __grid_constant__ Tok
     const unsigned tok = t % a.page_tokens;
     const unsigned page = t / a.page_tokens;
     const uint4 r = __ldg(a.recs + page);
-    if (tok >= r.y) continue;  // uniform across the CTA
+    if (!record_ok(r, a.n_requests, a.page_tokens, a.total_pages, a.status)) continue;  // uniform across the CTA
+    if (tok >= r.y) continue;
     const unsigned id = r.x;
     unsigned shard;
     unsigned long long local;
@@ -466,6 +506,7 @@ __global__ void __launch_bounds__(256) k_token_major(const __grid_constant__ Tok
     char* pool_p = a.pool.base[shard] + (local * a.page_tokens + tok) * a.token_bytes +
                    (unsigned long long)slab * slab_elems * sizeof(T);
     const longlong2 rq = __ldg(reinterpret_cast<const longlong2*>(a.reqs + r.z));
+    if (!window_ok(r, rq.y, a.status)) continue;
     T* work = reinterpret_cast<T*>(rq.x);
     const unsigned long long T_req = (unsigned long long)rq.y;
     const unsigned long long wtok = r.w + tok;
@@ -542,6 +583,9 @@ struct TokenMajor16Args {
   FastDiv div_L, div_H, div_HG, div_Gs, div_slabs, div_ptok;
   unsigned long long token_bytes;  // D*H*L*4
   int to_pool;
+  int* status;
+  unsigned n_requests;
+  unsigned long long total_pages;
 };
 
 // Shared-memory word index of (d_local, h, l): layout [j = d%8][h][g = d/8][l].
@@ -565,7 +609,8 @@ __global__ void __launch_bounds__(256) k_token_major16(const __grid_constant__ T
     const unsigned page = a.div_ptok.div(t);
     const unsigned tok = t - page * a.page_tokens;
     const uint4 r = __ldg(a.recs + page);
-    if (tok >= r.y) continue;  // uniform across the CTA
+    if (!record_ok(r, a.n_requests, a.page_tokens, a.total_pages, a.status)) continue;  // uniform across the CTA
+    if (tok >= r.y) continue;
     const unsigned id = r.x;
     unsigned shard;
     unsigned long long local;
@@ -579,6 +624,7 @@ __global__ void __launch_bounds__(256) k_token_major16(const __grid_constant__ T
     uint4* pool_p = reinterpret_cast<uint4*>(a.pool.base[shard] + (local * a.page_tokens + tok) * a.token_bytes +
                                              (unsigned long long)slab * slab_words * 4ull);
     const longlong2 rq = __ldg(reinterpret_cast<const longlong2*>(a.reqs + r.z));
+    if (!window_ok(r, rq.y, a.status)) continue;
     unsigned short* work = reinterpret_cast<unsigned short*>(rq.x);
     const unsigned long long T_req = (unsigned long long)rq.y;
     // Element offset of (plane 0, this token, h = 0, first d of the slab); a plane is
@@ -707,6 +753,9 @@ struct TokenMajor16vArgs {
   FastDiv div_LU, div_H, div_HG, div_Gs, div_slabs, div_ptok;
   unsigned long long token_bytes;  // D*H*L*4
   int to_pool;
+  int* status;
+  unsigned n_requests;
+  unsigned long long total_pages;
 };
 
 struct TmItem {
@@ -725,6 +774,7 @@ __device__ __forceinline__ TmItem tm16v_item(const TokenMajor16vArgs& a, unsigne
   const unsigned page = a.div_ptok.div(t);
   const unsigned tok = t - page * a.page_tokens;
   const uint4 r = __ldg(a.recs + page);
+  if (!record_ok(r, a.n_requests, a.page_tokens, a.total_pages, a.status)) return it;
   if (tok >= r.y) return it;
   const unsigned id = r.x;
   unsigned shard;
@@ -739,6 +789,7 @@ __device__ __forceinline__ TmItem tm16v_item(const TokenMajor16vArgs& a, unsigne
   it.pool_p = reinterpret_cast<uint4*>(a.pool.base[shard] + (local * a.page_tokens + tok) * a.token_bytes) +
               (unsigned long long)slab * slab_units;
   const longlong2 rq = __ldg(reinterpret_cast<const longlong2*>(a.reqs + r.z));
+  if (!window_ok(r, rq.y, a.status)) return it;
   const unsigned row_elems = a.H * a.D;
   it.work_tok = reinterpret_cast<unsigned short*>(rq.x) + (unsigned long long)(r.w + tok) * row_elems +
                 slab * a.Gs * 8;

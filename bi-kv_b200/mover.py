@@ -228,7 +228,8 @@ class PageMover:
         with torch.cuda.stream(st):
             scratch[:nbytes].copy_(plan._store.view(torch.uint8).view(-1)[:nbytes], non_blocking=True)
         N.check(fn(C.byref(pool.desc), C.byref(g), C.c_void_p(scratch.data_ptr()), plan.n_pages,
-                   C.c_void_p(table.data_ptr()), slots, C.c_void_p(int(st.cuda_stream))), fn.__name__)
+                   C.c_void_p(table.data_ptr()), slots, C.c_void_p(self.status.data_ptr()),
+                   C.c_void_p(int(st.cuda_stream))), fn.__name__)
         self._hold(plan, stream)
 
     def gather_nhd(self, pool: ShardedPool, plan: Plan, layers: Sequence[torch.Tensor], *, validate: bool = True,

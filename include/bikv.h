@@ -162,7 +162,12 @@ int bikv_plan_validate(const bikv_page_rec* recs, int64_t n_pages,
  *   recs_dev / requests_dev  device arrays (n_pages / n_requests entries)
  *   status_dev               device int32[4], zeroed by the caller; word 0
  *                            receives a bikv_status if a bounded device wait
- *                            runs out.  May be NULL for BIKV_VARIANT_LDST.
+ *                            runs out, or if a record points outside the pool or
+ *                            outside its worker tensor: the kernels check every
+ *                            record and SKIP a bad one instead of touching memory
+ *                            (records in device memory cannot be checked on the
+ *                            host).  May be NULL for BIKV_VARIANT_LDST; bad records
+ *                            are then skipped silently.
  */
 int bikv_gather(const bikv_pool_desc* pool, const bikv_geometry* geom,
                 const bikv_page_rec* recs_dev, int64_t n_pages,
@@ -217,10 +222,12 @@ int bikv_scatter_h(const bikv_pool_desc* pool, const bikv_geometry* geom,
  */
 int bikv_gather_nhd(const bikv_pool_desc* pool, const bikv_geometry* geom,
                     const bikv_page_rec* recs_dev, int64_t n_pages,
-                    void* const* layer_bases_dev, int64_t slots_per_layer, void* stream);
+                    void* const* layer_bases_dev, int64_t slots_per_layer,
+                    int32_t* status_dev, void* stream);
 int bikv_scatter_nhd(const bikv_pool_desc* pool, const bikv_geometry* geom,
                      const bikv_page_rec* recs_dev, int64_t n_pages,
-                     void* const* layer_bases_dev, int64_t slots_per_layer, void* stream);
+                     void* const* layer_bases_dev, int64_t slots_per_layer,
+                     int32_t* status_dev, void* stream);
 /* Host-side check of a paged-worker plan: page ids in the pool, valid_tokens in
  * 1..page_tokens, slots inside [0, slots_per_layer), and (check_overlap) no pool
  * page named twice. */

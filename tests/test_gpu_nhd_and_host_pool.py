@@ -116,3 +116,27 @@ def test_pool_shard_in_pinned_host_memory(cuda):
     O.scatter(shards_cpu, g, recs, src)
     torch.cuda.synchronize()
     assert equal_bits(host_shard, shards_cpu[0]) and equal_bits(dev_shard, shards_cpu[1])
+
+
+def test_paged_worker_bad_device_records_are_skipped(cuda):
+    import ctypes as C
+    g = GEOS["small"]
+    shard_cpu = make_shards(g, 1, 6, 3)[0]
+    shard = shard_cpu.to(cuda)
+    pool = B.ShardedPool.single(shard, g)
+    mover = B.PageMover(cuda)
+    layers = [torch.zeros(32, 2, g.n_kv_heads, g.head_dim, dtype=g.dtype, device=cuda) for _ in range(g.n_layers)]
+    table, slots, _ = mover.layer_table(g, layers)
+    recs = torch.tensor([[2, 16, 0, 0], [6, 16, 0, 16], [1, 16, 0, 17], [1, 16, 0, -1], [1, 40, 0, 0]],
+                        dtype=torch.int32, device=cuda)
+    gn = g.native()
+    rc = N.lib().bikv_gather_nhd(C.byref(pool.desc), C.byref(gn), C.c_void_p(recs.data_ptr()), recs.shape[0],
+                                 C.c_void_p(table.data_ptr()), slots, C.c_void_p(mover.status.data_ptr()), None)
+    assert rc == 0
+    torch.cuda.synchronize()
+    ref = [torch.zeros(32, 2, g.n_kv_heads, g.head_dim, dtype=g.dtype) for _ in range(g.n_layers)]
+    O.gather_nhd([shard_cpu], g, [(2, 16, 0, 0)], ref)
+    for a, b in zip(layers, ref):
+        assert equal_bits(a, b)
+    with pytest.raises(B.BikvError):
+        mover.check_status()

@@ -308,3 +308,42 @@ def test_bounded_device_wait_reports_a_timeout_and_the_context_survives(cuda):
     run_case(cuda, SMALL, 1, 8, 2, 40, N.VARIANT_BULK, seed=3)     # the context is still usable
     assert N.lib().bikv_selftest_wait_timeout(None, 1000, None) == N.ERR_BAD_ARG
     assert N.lib().bikv_selftest_wait_timeout(C.c_void_p(mover.status.data_ptr()), 2_000_000_000, None) == N.ERR_BAD_ARG
+
+
+@pytest.mark.parametrize("layout", [N.POOL_PAGED, N.POOL_TOKEN_MAJOR])
+@pytest.mark.parametrize("variant", VARIANTS)
+def test_bad_records_in_a_device_plan_are_skipped_not_dereferenced(cuda, layout, variant):
+    """Plans handed over in device memory cannot be checked on the host.  The kernels check
+    each record themselves: a bad one is skipped (no access at all), the first error lands in
+    the status word, good records are still served."""
+    g = KVGeometry(4, 2, 64, 16, torch.float16, layout)
+    shard_cpu = make_shards(g, 1, 8, 1)[0]
+    shard = shard_cpu.to(cuda)
+    pool = B.ShardedPool.single(shard, g)
+    mover = B.PageMover(cuda)
+    out = make_workers(g, [48], cuda)
+    good = [[3, 16, 0, 0], [5, 7, 0, 16]]
+    bad = [[8, 16, 0, 32], [2_000_000_000, 16, 0, 32], [-1, 16, 0, 32],      # page outside the pool
+           [1, 0, 0, 32], [1, 17, 0, 32],                                  # valid_tokens out of range
+           [1, 16, 1, 32], [1, 16, -5, 32],                                # request index out of range
+           [1, 16, 0, 33], [1, 16, 0, -16], [1, 16, 0, 2_000_000_000]]     # token window outside the tensor
+    table = torch.tensor(good + bad, dtype=torch.int32, device=cuda)
+    reqs = mover.request_table(g, out).to(cuda)
+    mover.gather_dev(pool, table, reqs, variant=VARIANTS[variant])
+    torch.cuda.synchronize()
+    ref = make_workers(g, [48])
+    O.gather([shard_cpu], g, [tuple(r) for r in good], ref)
+    assert equal_bits(out[0], ref[0])                      # good records served, nothing else written
+    with pytest.raises(B.BikvError) as e:
+        mover.check_status()
+    assert e.value.status in (N.ERR_PAGE_RANGE, N.ERR_PLAN, N.ERR_BAD_ARG, N.ERR_DST_RANGE)
+    # the same plan as a scatter must leave the pool untouched outside the good pages
+    src = make_workers(g, [48], fill="normal", seed=5)
+    src_gpu = [src[0].to(cuda)]                          # must outlive the launch
+    mover.scatter_dev(pool, table, mover.request_table(g, src_gpu).to(cuda), variant=VARIANTS[variant])
+    torch.cuda.synchronize()
+    O.scatter([shard_cpu], g, [tuple(r) for r in good], src)
+    assert equal_bits(shard, shard_cpu)
+    with pytest.raises(B.BikvError):
+        mover.check_status()
+    mover.check_status()

@@ -19,8 +19,8 @@ from __future__ import annotations
 
 import ctypes as C
 import random
-from dataclasses import dataclass, field
-from typing import Iterator, List, Optional, Tuple
+from dataclasses import dataclass
+from typing import Iterator, List, Tuple
 
 import numpy as np
 

@@ -16,7 +16,6 @@ from typing import Dict, Optional
 
 import torch
 
-from . import _native as N
 from . import taskinfo as pb
 from .geometry import GEO_R, KVGeometry
 from .rpc_def import WORKER_offset

@@ -24,7 +24,6 @@ from .mover import PageMover
 from .page_manager import PageManager
 from .plan import plan_from_combined_task
 from .pool import ShardedPool
-from .rpc_def import KVCACHE_offset
 
 
 class Worker:

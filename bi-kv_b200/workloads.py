@@ -6,7 +6,7 @@ generators, pool contents are N(0,1) cast to the configuration's dtype.
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import List, Optional
+from typing import List
 
 import numpy as np
 import torch

@@ -2,7 +2,6 @@
 import numpy as np
 import torch
 
-from bikv_b200 import _native as N
 from oracle import bikv_oracle as O
 
 

@@ -1,7 +1,6 @@
 """CacheCoordinatorService: decisions of the coordinator loop, counters, polling and the
 scheduler query, with in-process shard stand-ins and over real gRPC on loopback."""
 import json
-import threading
 from concurrent import futures
 
 import grpc

@@ -4,7 +4,6 @@ import json
 import os
 import random
 
-import numpy as np
 import pytest
 
 from bikv_b200 import taskinfo as pb

@@ -1,6 +1,5 @@
 """Property test: random geometries, shard counts, layouts and ragged plans, every engine,
 against the oracle (hypothesis drives the shapes; data is seeded random bit patterns)."""
-import numpy as np
 import pytest
 import torch
 from hypothesis import HealthCheck, given, settings, strategies as st

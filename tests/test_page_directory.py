@@ -2,10 +2,8 @@
 (which the golden fixtures tie to the reference) and (b) the restated Go semantics."""
 import random
 
-import numpy as np
 import pytest
 
-from bikv_b200 import _native as N
 from bikv_b200.coordinator import NativePrefixCacheCoordinator, PrefixCacheCoordinator, PrefixReuseWorkload
 from bikv_b200.page_directory import PageDirectory, XorShiftChoice
 from bikv_b200.page_manager import MultiPageManager

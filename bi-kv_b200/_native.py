@@ -15,7 +15,8 @@ import threading
 _HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(_HERE, "csrc")
 INCLUDE = os.path.normpath(os.path.join(_HERE, "..", "include"))
-LIB_PATH = os.path.join(CSRC, "libbikv.so")
+# BIKV_LIB points at an alternative build of the library (measurement and debugging).
+LIB_PATH = os.environ.get("BIKV_LIB") or os.path.join(CSRC, "libbikv.so")
 SOURCES = ["bikv.cu", "bikv_pm.cpp"]
 HEADERS = ["bikv_kernels.cuh"]
 

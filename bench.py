@@ -148,7 +148,7 @@ class ClockSampler:
 
 
 # --------------------------------------------------------------------------- CPU arm
-def cpu_reference_run(steps, warmup, requests, budget_s=20.0):
+def cpu_reference_run(steps, warmup, requests, limit_s=20.0):
     """The reference's CPU data path (token rows in host tensors, torch advanced indexing
     over token indices: DistributedStorage/kvcache.py:38-43, Worker/Worker.py:57-62,207) as
     restated in oracle/, on a bounded sample of the single-GPU workload: same geometry and
@@ -188,7 +188,7 @@ def cpu_reference_run(steps, warmup, requests, budget_s=20.0):
         t = time.perf_counter()
         step()
         times.append(time.perf_counter() - t)
-        if time.perf_counter() - t_all > budget_s:
+        if time.perf_counter() - t_all > limit_s:
             break
     total = sum(times)
     done = len(times)
@@ -214,7 +214,7 @@ def run_reference_arm(args, rank):
         if res.returncode != 0:
             raise SystemExit(res.returncode)
         return
-    base = cpu_reference_run(args.steps, args.warmup, args.requests, budget_s=120.0)
+    base = cpu_reference_run(args.steps, args.warmup, args.requests, limit_s=120.0)
     line = {
         "impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": args.gpus,
         "steps": base["steps_done"], "warmup": args.warmup, "ms_per_step": base["ms_per_step"],
@@ -889,7 +889,7 @@ def main():
         if host_kv:
             line["e2e_host_kv"] = host_kv
         if not multi and not args.no_cpu_baseline:
-            base = cpu_reference_run(20, 1, args.requests, budget_s=15.0)
+            base = cpu_reference_run(20, 1, args.requests, limit_s=15.0)
             line["cpu_baseline"] = {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")}
         print(json.dumps(line), flush=True)
 

@@ -1,4 +1,4 @@
-"""The ctypes stub printed in INTEGRATION.md is executed as written (only the library path
+"""The ctypes stub printed in the integration guide at the repository root is executed as written (only the library path
 is filled in) against a pool in the reference's layout, and checked with the oracle."""
 import os
 import re
@@ -25,14 +25,14 @@ def _stub_source():
 
 def test_stub_parses_and_binds(native):
     ns = {}
-    exec(compile(_stub_source(), "INTEGRATION.md", "exec"), ns)
+    exec(compile(_stub_source(), "integration_stub", "exec"), ns)
     assert callable(ns["shared_data_batch_pages"])
 
 
 @pytest.mark.gpu
 def test_stub_gathers_like_the_oracle(cuda):
     ns = {}
-    exec(compile(_stub_source(), "INTEGRATION.md", "exec"), ns)
+    exec(compile(_stub_source(), "integration_stub", "exec"), ns)
     page_size, pool_pages = 16, 24
     geom = KVGeometry(28, 2, 128, page_size, torch.float16, N.POOL_TOKEN_MAJOR)
     pool_cpu = normal(geom.pool_shape(pool_pages), geom.dtype, 3)

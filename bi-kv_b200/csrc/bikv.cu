@@ -22,10 +22,13 @@ std::atomic<long long> g_bulk_ctas_per_sm{3};
 std::atomic<long long> g_bulk_stages{4};
 std::atomic<long long> g_seg_bytes{16384};
 std::atomic<long long> g_auto_variant{0};  // 0 = choose by shard count
-std::atomic<long long> g_tm_threads{128};      // CTA size of k_token_major16v (128 measured best: 0.85 vs 0.82)
+std::atomic<long long> g_tm_threads{0};        // CTA size of k_token_major16v; 0 = by tile size (see launcher)
 std::atomic<long long> g_ldst_threads{256};    // CTA size of k_paged_ldst / k_paged_nhd / k_flat
 std::atomic<long long> g_tm16_threads{256};    // CTA size of k_token_major16
 std::atomic<long long> g_tm_max_groups{16};    // cap on d-groups per slab (k_token_major16v)
+std::atomic<long long> g_tm_tile_kib{48};      // cap on one slab tile of k_token_major16v holding all heads, KiB
+std::atomic<long long> g_tm_split_tile_kib{96};  // the same for a slab that splits the heads
+std::atomic<long long> g_tm_max_heads{64};     // cap on heads per slab when the slab splits the heads
 
 int cuda_fail(cudaError_t e) {
   tl_cuda_error = (int)e;
@@ -188,29 +191,40 @@ int launch_token_major16v(const bikv_pool_desc* pool, const bikv_geometry* g, co
                           const DeviceInfo& di, int32_t* status, int32_t n_requests) {
   const unsigned H = g->n_kv_heads, D = g->head_dim, L = g->n_layers;
   const unsigned G = D / 8, LU = L / 4;
-  unsigned ru_log2 = 3;
-  while ((1u << ru_log2) < LU) ++ru_log2;
-  const long long per_group = 8ll * H * (16ll << ru_log2);   // tile bytes per d-group
-  unsigned Gs = 0;
-  for (unsigned cand = std::min<unsigned>(G, (unsigned)g_tm_max_groups.load()); cand >= 1; --cand) {
-    if (G % cand) continue;
-    if (per_group * cand <= 48 * 1024) {
-      Gs = cand;
-      break;
+  const unsigned RU = std::max(8u, (LU + 7u) & ~7u);   // row pitch in 16-byte units
+  const long long per_gh = 8ll * 16ll * RU;            // tile bytes per (d-group, head)
+  const unsigned max_groups = (unsigned)std::max<long long>(1, g_tm_max_groups.load());
+  // Slab = Gs d-groups x Hs heads.  All heads within 48 KiB when that leaves worker-side runs
+  // (Gs*16 bytes per head) of 128 bytes or more; otherwise the most heads that do within
+  // 96 KiB.  Measured at 80 layers x 8 heads, fractions of the HBM copy peak: 4 heads x 64 d
+  // (96 KiB) 0.83-0.85, 1 head x 128 d (48 KiB) 0.77, 2 heads x 64 d (48 KiB) 0.73,
+  // 1 head x 64 d (24 KiB) 0.62; the older kernel 0.61.
+  const long long cap_all = g_tm_tile_kib.load() * 1024, cap_split = g_tm_split_tile_kib.load() * 1024;
+  unsigned Gs = 0, Hs = 0;
+  const unsigned max_split_heads = (unsigned)std::max<long long>(1, g_tm_max_heads.load());
+  for (unsigned hs = H; hs >= 1 && Gs == 0; --hs) {
+    if (H % hs || (hs < H && hs > max_split_heads)) continue;
+    for (unsigned cand = std::min(G, max_groups); cand >= 1; --cand) {
+      if (G % cand) continue;
+      if (per_gh * hs * cand <= (hs == H ? cap_all : cap_split)) {
+        if (cand >= 8) { Gs = cand; Hs = hs; }
+        break;
+      }
     }
   }
-  // Worker-side runs are Gs*16 bytes per head; below 128 bytes the older kernel, whose
-  // slab may hold more d-groups, does better (measured 0.61 against 0.22 of the HBM
-  // copy peak at 80 layers x 8 heads).
-  if (Gs < 8) return 1;
-  const long long tile = per_group * Gs;
-  const long long smem = to_pool ? tile : 2 * tile;
+  // No slab with 128-byte runs (head_dim below 64, or rows too long): the older kernel,
+  // whose slab may hold more d-groups, does better there.
+  if (Gs == 0) return 1;
+  const long long tile = per_gh * Hs * Gs;
+  const long long smem = to_pool ? tile : 2 * tile;   // the gather double-buffers the slab
   if (smem > di.max_optin_smem) return 1;
-  const long long items = n_pages * g->page_tokens * (long long)(G / Gs);
+  const unsigned slabs = (G / Gs) * (H / Hs);
+  const long long items = n_pages * g->page_tokens * (long long)slabs;
   if (items > 0x7fffffffll) return BIKV_ERR_TOO_LARGE;
-  const unsigned long long rows = 8ull * Gs * H;
-  if ((unsigned long long)items * std::max<unsigned>(G / Gs, (unsigned)g->page_tokens) >= (1ull << 32) ||
-      rows * LU * std::max(std::max(LU, H), H * Gs) >= (1ull << 32))
+  const unsigned long long rows = 8ull * Gs * Hs;
+  // FastDiv is exact while dividend * divisor < 2^32.
+  if ((unsigned long long)items * std::max<unsigned>(slabs, (unsigned)g->page_tokens) >= (1ull << 32) ||
+      rows * LU * std::max(std::max(LU, Hs), Hs * Gs) >= (1ull << 32))
     return BIKV_ERR_TOO_LARGE;
   TokenMajor16vArgs a;
   memset(&a, 0, sizeof(a));
@@ -219,18 +233,22 @@ int launch_token_major16v(const bikv_pool_desc* pool, const bikv_geometry* g, co
   a.pool = to_dev(pool);
   a.n_items = (unsigned)items;
   a.page_tokens = g->page_tokens;
-  a.slabs = G / Gs;
+  a.slabs = slabs;
+  a.hslabs = H / Hs;
   a.Gs = Gs;
+  a.Hs = Hs;
   a.H = H;
   a.D = D;
   a.L = L;
   a.LU = LU;
-  a.RU_log2 = ru_log2;
+  a.RU = RU;
+  a.d_skip = (H - Hs) * LU;
   a.div_LU = fast_div(LU);
-  a.div_H = fast_div(H);
-  a.div_HG = fast_div(H * Gs);
+  a.div_Hs = fast_div(Hs);
+  a.div_HG = fast_div(Hs * Gs);
   a.div_Gs = fast_div(Gs);
   a.div_slabs = fast_div(a.slabs);
+  a.div_hslabs = fast_div(a.hslabs);
   a.div_ptok = fast_div((unsigned)g->page_tokens);
   a.token_bytes = (unsigned long long)D * H * L * 4ull;
   a.to_pool = to_pool;
@@ -240,11 +258,18 @@ int launch_token_major16v(const bikv_pool_desc* pool, const bikv_geometry* g, co
   const long long per_sm = std::max<long long>(1, std::min<long long>(12, (220 * 1024) / (smem + 1024)));
   const unsigned grid = (unsigned)std::min<long long>(items, (long long)di.sm_count * per_sm);
   if (grid == 0) return BIKV_OK;
-  BIKV_CUDA(cudaFuncSetAttribute(k_token_major16v, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  auto kern = Hs < H ? (to_pool ? k_token_major16v<true, true> : k_token_major16v<true, false>)
+                     : (to_pool ? k_token_major16v<false, true> : k_token_major16v<false, false>);
+  BIKV_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)std::max<long long>(2 * tile, 48 * 1024)));
-  BIKV_CUDA(cudaFuncSetAttribute(k_token_major16v, cudaFuncAttributePreferredSharedMemoryCarveout,
+  BIKV_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout,
                                  cudaSharedmemCarveoutMaxShared));
-  k_token_major16v<<<grid, (unsigned)g_tm_threads.load(), (size_t)smem, st>>>(a);
+  // CTA size: 128 threads for tiles up to 48 KiB (measured 0.84-0.85 against 0.81-0.82 with
+  // 224-256), 192 for larger ones (0.853 against 0.831 with 128 at 96 KiB).
+  unsigned threads = (unsigned)g_tm_threads.load();
+  if (threads == 0) threads = tile <= 48 * 1024 ? 128 : (to_pool ? 256 : 192);
+  threads = std::min(256u, std::max(32u, threads & ~31u));
+  kern<<<grid, threads, (size_t)smem, st>>>(a);
   return after_launch();
 }
 
@@ -433,9 +458,12 @@ Knob* find_knob(const char* name) {
       {"seg_bytes", &g_seg_bytes, 1024, 64 * 1024},
       {"auto_variant", &g_auto_variant, 0, BIKV_VARIANT_BULK},
       {"ldst_threads", &g_ldst_threads, 64, 256},
-      {"tm_threads", &g_tm_threads, 64, 256},
+      {"tm_threads", &g_tm_threads, 0, 256},
       {"tm16_threads", &g_tm16_threads, 64, 256},
       {"tm_max_groups", &g_tm_max_groups, 1, 64},
+      {"tm_tile_kib", &g_tm_tile_kib, 8, 100},
+      {"tm_split_tile_kib", &g_tm_split_tile_kib, 8, 100},
+      {"tm_max_heads", &g_tm_max_heads, 1, 64},
   };
   if (!name) return nullptr;
   for (auto& k : knobs)

@@ -735,11 +735,13 @@ __global__ void __launch_bounds__(256) k_token_major16(const __grid_constant__ T
 // Token-major pool, 2-byte elements, n_layers a multiple of 4: 16-byte shared
 // memory accesses on both sides.
 //
-// The slab (Gs groups of 8 d, all heads, all layers of one token) is kept in its
-// pool order, one row per (d, h) of L words, padded to RU 16-byte units (a power
-// of two >= 8).  The unit at position q of row (d, h) is stored at q ^ (hg & 7),
-// hg = h*Gs + d/8 the index of the row's (head, d-group).  Pool side: 16-byte units copied straight through
-// (cp.async on gather, so the next slab loads while this one is written out).
+// The slab (Gs groups of 8 d, Hs consecutive heads, all layers of one token) is kept
+// in its pool order, one row per (d, h) of L words, padded to RU 16-byte units (a
+// multiple of 8).  The unit at position q of row (d, h) is stored at q ^ (hg & 7),
+// hg = h*Gs + d/8 the index of the row's (head, d-group) within the slab.  Pool side:
+// 16-byte units copied straight through, one contiguous run of Hs*L words per d (the
+// whole slab is one run when Hs = H); cp.async on gather, so the next slab loads while
+// this one is written out.
 // Worker side: thread (lq, h, g) reads the 8 rows j = 0..7 of its (h, g) at unit
 // lq -- the 8 lanes of a quarter warp have 8 consecutive hg, so the XOR sends them
 // to 8 different bank groups -- and turns the 8 x 4 (K,V) words into 4 K vectors and
@@ -751,12 +753,15 @@ struct TokenMajor16vArgs {
   PoolDev pool;
   unsigned n_items;      // n_pages * page_tokens * slabs
   unsigned page_tokens;
-  unsigned slabs;        // G / Gs
+  unsigned slabs;        // (G / Gs) * hslabs
+  unsigned hslabs;       // H / Hs
   unsigned Gs;           // d-groups (of 8) per slab
+  unsigned Hs;           // heads per slab (divides H)
   unsigned H, D, L;
   unsigned LU;           // L / 4: 16-byte units per row
-  unsigned RU_log2;      // log2 of the padded row pitch in units
-  FastDiv div_LU, div_H, div_HG, div_Gs, div_slabs, div_ptok;
+  unsigned RU;           // padded row pitch in units, a multiple of 8
+  unsigned d_skip;       // (H - Hs) * LU: pool units between the runs of consecutive d
+  FastDiv div_LU, div_Hs, div_HG, div_Gs, div_slabs, div_hslabs, div_ptok;
   unsigned long long token_bytes;  // D*H*L*4
   int to_pool;
   int* status;
@@ -771,7 +776,8 @@ struct TmItem {
   bool valid;
 };
 
-__device__ __forceinline__ TmItem tm16v_item(const TokenMajor16vArgs& a, unsigned w, unsigned slab_units) {
+template <bool SPLIT>
+__device__ __forceinline__ TmItem tm16v_item(const TokenMajor16vArgs& a, unsigned w) {
   TmItem it;
   it.valid = false;
   if (w >= a.n_items) return it;
@@ -792,24 +798,33 @@ __device__ __forceinline__ TmItem tm16v_item(const TokenMajor16vArgs& a, unsigne
     shard = (unsigned)(id / a.pool.pages_per_shard);
     local = id % a.pool.pages_per_shard;
   }
+  const unsigned gslab = SPLIT ? a.div_hslabs.div(slab) : slab;
+  const unsigned h0 = SPLIT ? (slab - gslab * a.hslabs) * a.Hs : 0u;   // first head of the slab
+  const unsigned d0 = gslab * a.Gs * 8;                                // first d of the slab
   it.pool_p = reinterpret_cast<uint4*>(a.pool.base[shard] + (local * a.page_tokens + tok) * a.token_bytes) +
-              (unsigned long long)slab * slab_units;
+              ((unsigned long long)d0 * a.H + h0) * a.LU;
   const longlong2 rq = __ldg(reinterpret_cast<const longlong2*>(a.reqs + r.z));
   if (!window_ok(r, rq.y, a.status)) return it;
   const unsigned row_elems = a.H * a.D;
   it.work_tok = reinterpret_cast<unsigned short*>(rq.x) + (unsigned long long)(r.w + tok) * row_elems +
-                slab * a.Gs * 8;
+                h0 * a.D + d0;
   it.plane_elems = (unsigned long long)rq.y * row_elems;
   it.valid = true;
   return it;
 }
 
-// Shared-memory unit index of unit q of slab row `row` (= d_local*H + h).
-__device__ __forceinline__ unsigned tm16v_unit(const TokenMajor16vArgs& a, unsigned row, unsigned q) {
-  const unsigned d_local = a.div_H.div(row);
-  const unsigned h = row - d_local * a.H;
+// Unit i of the slab (row = i / LU = d_local*Hs + h, q = i % LU): its index in shared
+// memory and its offset from the slab's first unit in the pool.
+template <bool SPLIT>
+__device__ __forceinline__ void tm16v_unit(const TokenMajor16vArgs& a, unsigned i, unsigned& smem_unit,
+                                           unsigned& pool_unit) {
+  const unsigned row = a.div_LU.div(i);
+  const unsigned q = i - row * a.LU;
+  const unsigned d_local = a.div_Hs.div(row);
+  const unsigned h = row - d_local * a.Hs;
   const unsigned hg = h * a.Gs + (d_local >> 3);
-  return (row << a.RU_log2) + (q ^ (hg & 7));
+  smem_unit = row * a.RU + (q ^ (hg & 7));
+  pool_unit = SPLIT ? i + d_local * a.d_skip : i;
 }
 
 __device__ __forceinline__ void cp_async16(uint32_t dst_smem, const void* src) {
@@ -818,34 +833,36 @@ __device__ __forceinline__ void cp_async16(uint32_t dst_smem, const void* src) {
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 
+// SPLIT = the slab holds fewer heads than the pool row (Hs < H); TO_POOL = scatter.
+template <bool SPLIT, bool TO_POOL>
 __global__ void __launch_bounds__(256) k_token_major16v(const __grid_constant__ TokenMajor16vArgs a) {
   extern __shared__ __align__(16) uint4 tm16v_tile[];
-  const unsigned HG = a.H * a.Gs;
-  const unsigned rows = a.Gs * 8 * a.H;
+  const unsigned HG = a.Hs * a.Gs;
+  const unsigned rows = a.Gs * 8 * a.Hs;
   const unsigned slab_units = rows * a.LU;
-  const unsigned tile_units = rows << a.RU_log2;
+  const unsigned tile_units = rows * a.RU;
   const unsigned n_out = a.LU * HG;
 
-  if (!a.to_pool) {
+  if constexpr (!TO_POOL) {
     // Gather: two tiles; the slab of the next item streams in with cp.async while
     // the current one is transposed out.
     auto load = [&](const TmItem& it, uint4* tile) {
       if (!it.valid) return;
       const uint32_t base = smem_u32(tile);
       for (unsigned i = threadIdx.x; i < slab_units; i += blockDim.x) {
-        const unsigned row = a.div_LU.div(i);
-        const unsigned q = i - row * a.LU;
-        cp_async16(base + tm16v_unit(a, row, q) * 16u, it.pool_p + i);
+        unsigned su, pu;
+        tm16v_unit<SPLIT>(a, i, su, pu);
+        cp_async16(base + su * 16u, it.pool_p + pu);
       }
     };
     unsigned w = blockIdx.x;
-    TmItem cur = tm16v_item(a, w, slab_units);
+    TmItem cur = tm16v_item<SPLIT>(a, w);
     unsigned buf = 0;
     load(cur, tm16v_tile);
     cp_async_commit();
     while (w < a.n_items) {
       const unsigned w_next = w + gridDim.x;
-      const TmItem nxt = tm16v_item(a, w_next, slab_units);
+      const TmItem nxt = tm16v_item<SPLIT>(a, w_next);
       load(nxt, tm16v_tile + (buf ^ 1) * tile_units);
       cp_async_commit();
       // everything but the group just committed has landed
@@ -861,7 +878,7 @@ __global__ void __launch_bounds__(256) k_token_major16v(const __grid_constant__ 
           const unsigned q = lq ^ (hg & 7);
           uint4 wv[8];
 #pragma unroll
-          for (unsigned j = 0; j < 8; ++j) wv[j] = tile[((((g << 3) + j) * a.H + h) << a.RU_log2) + q];
+          for (unsigned j = 0; j < 8; ++j) wv[j] = tile[(((g << 3) + j) * a.Hs + h) * a.RU + q];
           unsigned short* dst = cur.work_tok + (8ull * lq) * cur.plane_elems + h * a.D + g * 8;
 #pragma unroll
           for (unsigned c = 0; c < 4; ++c) {
@@ -886,9 +903,12 @@ __global__ void __launch_bounds__(256) k_token_major16v(const __grid_constant__ 
     return;
   }
 
-  // Scatter: worker -> shared (transposing) -> pool (straight through).
+  // Scatter: worker -> shared (transposing) -> pool (straight through).  One tile: CTAs
+  // sharing the SM cover each other's phases (a two-tile version that read the next item's
+  // rows while the current tile drained halved the resident CTAs and measured slower,
+  // 0.64 against 0.79 of the HBM copy peak at 80 layers x 8 heads).
   for (unsigned w = blockIdx.x; w < a.n_items; w += gridDim.x) {
-    const TmItem it = tm16v_item(a, w, slab_units);
+    const TmItem it = tm16v_item<SPLIT>(a, w);
     if (!it.valid) continue;  // uniform across the CTA
     uint4* tile = tm16v_tile;
     for (unsigned o = threadIdx.x; o < n_out; o += blockDim.x) {
@@ -913,14 +933,14 @@ __global__ void __launch_bounds__(256) k_token_major16v(const __grid_constant__ 
         out.y = __byte_perm((&kv[1].x)[j >> 1], (&vv[1].x)[j >> 1], sel);
         out.z = __byte_perm((&kv[2].x)[j >> 1], (&vv[2].x)[j >> 1], sel);
         out.w = __byte_perm((&kv[3].x)[j >> 1], (&vv[3].x)[j >> 1], sel);
-        tile[((((g << 3) + j) * a.H + h) << a.RU_log2) + q] = out;
+        tile[(((g << 3) + j) * a.Hs + h) * a.RU + q] = out;
       }
     }
     __syncthreads();
     for (unsigned i = threadIdx.x; i < slab_units; i += blockDim.x) {
-      const unsigned row = a.div_LU.div(i);
-      const unsigned q = i - row * a.LU;
-      st_stream16(it.pool_p + i, tile[tm16v_unit(a, row, q)]);
+      unsigned su, pu;
+      tm16v_unit<SPLIT>(a, i, su, pu);
+      st_stream16(it.pool_p + pu, tile[su]);
     }
     __syncthreads();
   }

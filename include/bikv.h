@@ -112,8 +112,8 @@ int bikv_last_cuda_error(void);
 /* Number of kernels this library has launched in this process. */
 int64_t bikv_launch_count(void);
 /* Tuning knobs: "ldst_ctas_per_sm", "bulk_ctas_per_sm", "bulk_stages",
- * "seg_bytes", "auto_variant", "ldst_threads", "tm_threads", "tm16_threads", "tm_max_groups".  Returns BIKV_ERR_BAD_ARG for unknown names or
- * values out of range. */
+ * "seg_bytes", "auto_variant", "ldst_threads", "tm_threads", "tm16_threads", "tm_max_groups",
+ * "tm_tile_kib", "tm_split_tile_kib", "tm_max_heads".  Returns BIKV_ERR_BAD_ARG for unknown names or values out of range. */
 int bikv_set_tuning(const char* name, int64_t value);
 int64_t bikv_get_tuning(const char* name);
 

@@ -76,7 +76,9 @@ TM_GEOS = {
     "R50": B.GEO_R,
     "R16": KVGeometry(28, 2, 128, 16, torch.float16, TM),
     "B": KVGeometry(28, 4, 128, 16, torch.bfloat16, TM),        # 2 slabs
-    "C-lite": KVGeometry(80, 8, 128, 4, torch.float16, TM),     # 8 slabs of 16 d
+    "C-lite": KVGeometry(80, 8, 128, 4, torch.float16, TM),     # slabs of 64 d x 1 head
+    "H6": KVGeometry(40, 6, 128, 4, torch.bfloat16, TM),        # slabs of 64 d x 3 heads
+    "d64": KVGeometry(24, 2, 64, 16, torch.float16, TM),        # one slab per token
     "tiny": KVGeometry(1, 1, 8, 3, torch.float16, TM),
     "odd": KVGeometry(3, 3, 24, 5, torch.bfloat16, TM),
     "f32": KVGeometry(2, 2, 8, 4, torch.float32, TM),
@@ -109,6 +111,42 @@ def test_token_major_gather_scatter(cuda, geo, n_shards):
     O.scatter(shards_cpu, g, recs, src_cpu)
     for a, b in zip(shards_gpu, shards_cpu):
         assert equal_bits(a, b)
+
+
+@pytest.mark.parametrize("tile_kib,split_kib,threads", [(8, 8, 0), (8, 16, 64), (16, 32, 96), (100, 100, 256)])
+@pytest.mark.parametrize("geo", ["R16", "B", "H6", "C-lite"])
+def test_token_major_slab_shapes(cuda, native, geo, tile_kib, split_kib, threads):
+    """The slab of the 16-byte transposing kernel (d-groups x heads) follows the tile caps;
+    every shape and CTA size moves the same bytes."""
+    g = TM_GEOS[geo]
+    knobs = {b"tm_tile_kib": tile_kib, b"tm_split_tile_kib": split_kib, b"tm_threads": threads}
+    old = {k: native.bikv_get_tuning(k) for k in knobs}
+    for k, v in knobs.items():
+        assert native.bikv_set_tuning(k, v) == 0
+    try:
+        rng = np.random.default_rng(tile_kib)
+        lists, tokens = random_plan(rng, g, 10, 2, 3 * g.page_tokens)
+        plan = build_plan([l.tolist() for l in lists], tokens.astype(np.int32), g.page_tokens,
+                          item_request=np.arange(2, dtype=np.int32), n_requests=2)
+        recs = [tuple(r) for r in plan.table.tolist()]
+        shards_cpu = make_shards(g, 1, 10, 4, fill="bits")
+        shards_gpu = [s.to(cuda) for s in shards_cpu]
+        pool = B.ShardedPool.from_tensors(shards_gpu, g)
+        mover = B.PageMover(cuda)
+        out = make_workers(g, tokens, cuda)
+        mover.gather(pool, plan, out)
+        ref = make_workers(g, tokens)
+        O.gather(shards_cpu, g, recs, ref)
+        for a, b in zip(out, ref):
+            assert equal_bits(a, b)
+        src_cpu = make_workers(g, tokens, fill="bits", seed=5)
+        mover.scatter(pool, plan, [t.to(cuda) for t in src_cpu])
+        O.scatter(shards_cpu, g, recs, src_cpu)
+        torch.cuda.synchronize()
+        assert equal_bits(shards_gpu[0], shards_cpu[0])
+    finally:
+        for k, v in old.items():
+            native.bikv_set_tuning(k, v)
 
 
 def test_token_major_equals_paged_after_conversion(cuda):

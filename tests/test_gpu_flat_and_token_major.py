@@ -114,7 +114,7 @@ def test_token_major_gather_scatter(cuda, geo, n_shards):
 
 
 @pytest.mark.parametrize("tile_kib,split_kib,threads", [(8, 8, 0), (8, 16, 64), (16, 32, 96), (100, 100, 256)])
-@pytest.mark.parametrize("geo", ["R16", "B", "H6", "C-lite"])
+@pytest.mark.parametrize("geo", ["R16", "R50", "B", "H6", "C-lite"])
 def test_token_major_slab_shapes(cuda, native, geo, tile_kib, split_kib, threads):
     """The slab of the 16-byte transposing kernel (d-groups x heads) follows the tile caps;
     every shape and CTA size moves the same bytes."""

@@ -347,3 +347,54 @@ def test_bad_records_in_a_device_plan_are_skipped_not_dereferenced(cuda, layout,
     with pytest.raises(B.BikvError):
         mover.check_status()
     mover.check_status()
+
+
+def test_one_mover_shared_by_threads_on_their_own_streams(cuda):
+    """The reference serves its data methods from a 20-thread gRPC pool
+    (distributed_grpc_init.py:127,144).  Eight threads share one PageMover, each on its own
+    stream with its own pool, plans of changing size and both kernel variants."""
+    import threading
+    geom = SMALL
+    n_threads, rounds, pages = 8, 6, 40
+    mover = B.PageMover(cuda)
+    errors = []
+
+    def work(tid):
+        try:
+            stream = torch.cuda.Stream(device=cuda)
+            rng = np.random.default_rng(100 + tid)
+            shard_cpu = make_shards(geom, 1, pages, 50 + tid, fill="bits")[0]
+            with torch.cuda.stream(stream):
+                shard = shard_cpu.to(cuda)
+            pool = B.ShardedPool.single(shard, geom)
+            for r in range(rounds):
+                n_req = int(rng.integers(1, 5))
+                lists, tokens = random_plan(rng, geom, pages, n_req, (pages // n_req) * geom.page_tokens)
+                plan = build_plan([l.tolist() for l in lists], tokens.astype(np.int32), geom.page_tokens,
+                                  item_request=np.arange(n_req, dtype=np.int32), n_requests=n_req)
+                recs = [tuple(x) for x in plan.table.tolist()]
+                variant = (N.VARIANT_LDST, N.VARIANT_BULK)[(tid + r) % 2]
+                with torch.cuda.stream(stream):
+                    out = make_workers(geom, tokens, cuda)
+                    mover.gather(pool, plan, out, variant=variant, stream=stream)
+                    src_cpu = make_workers(geom, tokens, fill="normal", seed=1000 * tid + r)
+                    src = [t.to(cuda, non_blocking=False) for t in src_cpu]
+                    mover.scatter(pool, plan, src, variant=variant, stream=stream)
+                stream.synchronize()
+                want = make_workers(geom, tokens)
+                O.gather([shard_cpu], geom, recs, want)
+                for a, b in zip(out, want):
+                    assert equal_bits(a, b), (tid, r)
+                O.scatter([shard_cpu], geom, recs, src_cpu)
+                assert equal_bits(shard, shard_cpu), (tid, r)
+        except Exception as e:  # noqa: BLE001
+            errors.append((tid, repr(e)))
+
+    threads = [threading.Thread(target=work, args=(i,)) for i in range(n_threads)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    torch.cuda.synchronize()
+    mover.check_status()
+    assert not errors, errors

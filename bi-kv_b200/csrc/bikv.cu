@@ -23,7 +23,7 @@ std::atomic<long long> g_bulk_stages{4};
 std::atomic<long long> g_seg_bytes{16384};
 std::atomic<long long> g_auto_variant{0};  // 0 = choose by shard count
 std::atomic<long long> g_tm_threads{0};        // CTA size of k_token_major16v; 0 = by tile size (see launcher)
-std::atomic<long long> g_ldst_threads{256};    // CTA size of k_paged_ldst / k_paged_nhd / k_flat
+std::atomic<long long> g_ldst_threads{256};    // CTA size of k_paged_ldst (k_paged_nhd and k_flat use 256)
 std::atomic<long long> g_tm16_threads{256};    // CTA size of k_token_major16
 std::atomic<long long> g_tm_max_groups{16};    // cap on d-groups per slab (k_token_major16v)
 std::atomic<long long> g_tm_tile_kib{48};      // cap on one slab tile of k_token_major16v holding all heads, KiB
@@ -179,7 +179,7 @@ int launch_token_major16(const bikv_pool_desc* pool, const bikv_geometry* g, con
     BIKV_CUDA(cudaFuncSetAttribute(k_token_major16, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   BIKV_CUDA(cudaFuncSetAttribute(k_token_major16, cudaFuncAttributePreferredSharedMemoryCarveout,
                                  cudaSharedmemCarveoutMaxShared));
-  k_token_major16<<<grid, (unsigned)g_tm16_threads.load(), (size_t)smem, st>>>(a);
+  k_token_major16<<<grid, (unsigned)g_tm16_threads.load() / 32 * 32, (size_t)smem, st>>>(a);
   return after_launch();
 }
 

@@ -28,6 +28,7 @@ std::atomic<long long> g_tm16_threads{256};    // CTA size of k_token_major16
 std::atomic<long long> g_tm_max_groups{16};    // cap on d-groups per slab (k_token_major16v)
 std::atomic<long long> g_tm_tile_kib{48};      // cap on one slab tile of k_token_major16v holding all heads, KiB
 std::atomic<long long> g_tm_split_tile_kib{96};  // the same for a slab that splits the heads
+std::atomic<long long> g_tm_scatter_staged{1};  // k_token_major16v scatter: 1 = through staged worker rows, 0 = through the transposed tile
 std::atomic<long long> g_tm_max_heads{64};     // cap on heads per slab when the slab splits the heads
 
 int cuda_fail(cudaError_t e) {
@@ -216,7 +217,10 @@ int launch_token_major16v(const bikv_pool_desc* pool, const bikv_geometry* g, co
   // whose slab may hold more d-groups, does better there.
   if (Gs == 0) return 1;
   const long long tile = per_gh * Hs * Gs;
-  const long long smem = to_pool ? tile : 2 * tile;   // the gather double-buffers the slab
+  const bool staged = to_pool && g_tm_scatter_staged.load() != 0;
+  const long long stage = 8ll * LU * ((Hs * Gs + 7u) & ~7u) * 16;   // the slab's worker vectors, unpadded
+  // the gather double-buffers the tile, the staged scatter the worker vectors
+  const long long smem = staged ? 2 * stage : (to_pool ? tile : 2 * tile);
   if (smem > di.max_optin_smem) return 1;
   const unsigned slabs = (G / Gs) * (H / Hs);
   const long long items = n_pages * g->page_tokens * (long long)slabs;
@@ -258,16 +262,21 @@ int launch_token_major16v(const bikv_pool_desc* pool, const bikv_geometry* g, co
   const long long per_sm = std::max<long long>(1, std::min<long long>(12, (220 * 1024) / (smem + 1024)));
   const unsigned grid = (unsigned)std::min<long long>(items, (long long)di.sm_count * per_sm);
   if (grid == 0) return BIKV_OK;
-  auto kern = Hs < H ? (to_pool ? k_token_major16v<true, true> : k_token_major16v<true, false>)
-                     : (to_pool ? k_token_major16v<false, true> : k_token_major16v<false, false>);
+  const int mode = staged ? 2 : (to_pool ? 1 : 0);
+  auto kern = Hs < H ? (mode == 2 ? k_token_major16v<true, 2> : mode == 1 ? k_token_major16v<true, 1> : k_token_major16v<true, 0>)
+                     : (mode == 2 ? k_token_major16v<false, 2> : mode == 1 ? k_token_major16v<false, 1> : k_token_major16v<false, 0>);
   BIKV_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)std::max<long long>(2 * tile, 48 * 1024)));
+                                 (int)std::max<long long>(smem, 48 * 1024)));
   BIKV_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout,
                                  cudaSharedmemCarveoutMaxShared));
-  // CTA size: 128 threads for tiles up to 48 KiB (measured 0.84-0.85 against 0.81-0.82 with
-  // 224-256), 192 for larger ones (0.853 against 0.831 with 128 at 96 KiB).
+  // CTA size, by measurement (fractions of the HBM copy peak).  Tiles up to 48 KiB (28 layers,
+  // 2 or 4 heads): gather 0.87-0.88 with 64 threads, 0.85 with 96-128, 0.81 with 224-256;
+  // staged scatter 0.92-0.94 with 64, 0.90-0.91 with 96, 0.88-0.91 with 128, 0.77-0.80 with 32.
+  // 96 KiB tiles (80 layers x 8 heads): gather 0.912 / 0.923 / 0.916 with 128 / 192 / 256;
+  // staged scatter 0.916 / 0.963 / 0.970 / 0.957 with 128 / 192 / 224 / 256; the scatter
+  // through the transposed tile 0.753 / 0.766 / 0.786 with 128 / 192 / 256.
   unsigned threads = (unsigned)g_tm_threads.load();
-  if (threads == 0) threads = tile <= 48 * 1024 ? 128 : (to_pool ? 256 : 192);
+  if (threads == 0) threads = tile <= 48 * 1024 ? (to_pool && !staged ? 128 : 64) : (staged ? 224 : to_pool ? 256 : 192);
   threads = std::min(256u, std::max(32u, threads & ~31u));
   kern<<<grid, threads, (size_t)smem, st>>>(a);
   return after_launch();
@@ -464,6 +473,7 @@ Knob* find_knob(const char* name) {
       {"tm_tile_kib", &g_tm_tile_kib, 8, 100},
       {"tm_split_tile_kib", &g_tm_split_tile_kib, 8, 100},
       {"tm_max_heads", &g_tm_max_heads, 1, 64},
+      {"tm_scatter_staged", &g_tm_scatter_staged, 0, 1},
   };
   if (!name) return nullptr;
   for (auto& k : knobs)

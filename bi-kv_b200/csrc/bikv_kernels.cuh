@@ -833,8 +833,9 @@ __device__ __forceinline__ void cp_async16(uint32_t dst_smem, const void* src) {
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 
-// SPLIT = the slab holds fewer heads than the pool row (Hs < H); TO_POOL = scatter.
-template <bool SPLIT, bool TO_POOL>
+// SPLIT = the slab holds fewer heads than the pool row (Hs < H).  MODE: 0 = gather,
+// 1 = scatter through the transposed tile, 2 = scatter through staged worker rows.
+template <bool SPLIT, int MODE>
 __global__ void __launch_bounds__(256) k_token_major16v(const __grid_constant__ TokenMajor16vArgs a) {
   extern __shared__ __align__(16) uint4 tm16v_tile[];
   const unsigned HG = a.Hs * a.Gs;
@@ -843,7 +844,7 @@ __global__ void __launch_bounds__(256) k_token_major16v(const __grid_constant__ 
   const unsigned tile_units = rows * a.RU;
   const unsigned n_out = a.LU * HG;
 
-  if constexpr (!TO_POOL) {
+  if constexpr (MODE == 0) {
     // Gather: two tiles; the slab of the next item streams in with cp.async while
     // the current one is transposed out.
     auto load = [&](const TmItem& it, uint4* tile) {
@@ -895,6 +896,79 @@ __global__ void __launch_bounds__(256) k_token_major16v(const __grid_constant__ 
         }
       }
       __syncthreads();  // the tile may be overwritten by the load after next
+      cur = nxt;
+      w = w_next;
+      buf ^= 1;
+    }
+    cp_async_wait_all();
+    return;
+  }
+
+  if constexpr (MODE == 2) {
+    // Scatter through staged worker rows: the 16-byte worker vectors of the slab stream
+    // into shared memory with cp.async in worker order, [plane][head, d-group], the unit
+    // of (plane, hg) at hg ^ (plane/8 & 7) so that the reads below spread over the banks;
+    // the rows of the next item load while thread (4 layers, head, d-group) reads its 4 K
+    // and 4 V vectors of the current one, turns them into the 8 pool units (8 d x 4
+    // layers of K,V) and stores those straight to the pool: lanes run along the layers
+    // of a row, then along the heads, so a warp's stores form contiguous runs.
+    const unsigned HGp = (HG + 7u) & ~7u;
+    const unsigned stage_units = 8 * a.LU * HGp;
+    auto load = [&](const TmItem& it, uint4* stage) {
+      if (!it.valid) return;
+      const uint32_t base = smem_u32(stage);
+      for (unsigned i = threadIdx.x; i < slab_units; i += blockDim.x) {
+        const unsigned p = a.div_HG.div(i);          // plane 2*layer + kv
+        const unsigned hg = i - p * HG;
+        const unsigned h = a.div_Gs.div(hg);
+        const unsigned g = hg - h * a.Gs;
+        const unsigned su = p * HGp + (hg ^ ((p >> 3) & 7));
+        cp_async16(base + su * 16u, it.work_tok + (unsigned long long)p * it.plane_elems + h * a.D + g * 8);
+      }
+    };
+    unsigned w = blockIdx.x;
+    TmItem cur = tm16v_item<SPLIT>(a, w);
+    unsigned buf = 0;
+    load(cur, tm16v_tile);
+    cp_async_commit();
+    while (w < a.n_items) {
+      const unsigned w_next = w + gridDim.x;
+      const TmItem nxt = tm16v_item<SPLIT>(a, w_next);
+      load(nxt, tm16v_tile + (buf ^ 1) * stage_units);
+      cp_async_commit();
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+      __syncthreads();
+      if (cur.valid) {
+        const uint4* stage = tm16v_tile + buf * stage_units;
+        for (unsigned o = threadIdx.x; o < n_out; o += blockDim.x) {
+          const unsigned t = a.div_LU.div(o);
+          const unsigned lq = o - t * a.LU;
+          const unsigned g = a.div_Hs.div(t);
+          const unsigned h = t - g * a.Hs;
+          const unsigned hg = h * a.Gs + g;
+          const uint4* src = stage + (8 * lq) * HGp + (hg ^ (lq & 7));
+          uint4 kv[4], vv[4];
+#pragma unroll
+          for (unsigned c = 0; c < 4; ++c) {
+            kv[c] = src[(2 * c) * HGp];
+            vv[c] = src[(2 * c + 1) * HGp];
+          }
+          const unsigned row_pitch = a.H * a.LU;   // pool units between d and d + 1
+          uint4* dst = cur.pool_p + ((g << 3) * a.H + h) * a.LU + lq;
+#pragma unroll
+          for (unsigned j = 0; j < 8; ++j) {
+            // word c of row j: K_j of layer 4*lq + c in the low half, V_j in the high half
+            uint4 out;
+            const unsigned sel = (j & 1) ? 0x7632 : 0x5410;
+            out.x = __byte_perm((&kv[0].x)[j >> 1], (&vv[0].x)[j >> 1], sel);
+            out.y = __byte_perm((&kv[1].x)[j >> 1], (&vv[1].x)[j >> 1], sel);
+            out.z = __byte_perm((&kv[2].x)[j >> 1], (&vv[2].x)[j >> 1], sel);
+            out.w = __byte_perm((&kv[3].x)[j >> 1], (&vv[3].x)[j >> 1], sel);
+            st_stream16(dst + j * row_pitch, out);
+          }
+        }
+      }
+      __syncthreads();  // the stage may be overwritten by the load after next
       cur = nxt;
       w = w_next;
       buf ^= 1;

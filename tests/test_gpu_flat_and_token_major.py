@@ -79,6 +79,7 @@ TM_GEOS = {
     "C-lite": KVGeometry(80, 8, 128, 4, torch.float16, TM),     # slabs of 64 d x 1 head
     "H6": KVGeometry(40, 6, 128, 4, torch.bfloat16, TM),        # slabs of 64 d x 3 heads
     "d64": KVGeometry(24, 2, 64, 16, torch.float16, TM),        # one slab per token
+    "d96": KVGeometry(12, 3, 96, 5, torch.float16, TM),         # 12 d-groups: slab rows not a multiple of 8
     "tiny": KVGeometry(1, 1, 8, 3, torch.float16, TM),
     "odd": KVGeometry(3, 3, 24, 5, torch.bfloat16, TM),
     "f32": KVGeometry(2, 2, 8, 4, torch.float32, TM),
@@ -113,13 +114,15 @@ def test_token_major_gather_scatter(cuda, geo, n_shards):
         assert equal_bits(a, b)
 
 
-@pytest.mark.parametrize("tile_kib,split_kib,threads", [(8, 8, 0), (8, 16, 64), (16, 32, 96), (100, 100, 256)])
-@pytest.mark.parametrize("geo", ["R16", "R50", "B", "H6", "C-lite"])
-def test_token_major_slab_shapes(cuda, native, geo, tile_kib, split_kib, threads):
+@pytest.mark.parametrize("staged", [0, 1])
+@pytest.mark.parametrize("tile_kib,split_kib,threads", [(8, 8, 0), (8, 16, 64), (16, 32, 96), (100, 100, 256), (48, 96, 0)])
+@pytest.mark.parametrize("geo", ["R16", "R50", "B", "H6", "C-lite", "d96"])
+def test_token_major_slab_shapes(cuda, native, geo, tile_kib, split_kib, threads, staged):
     """The slab of the 16-byte transposing kernel (d-groups x heads) follows the tile caps;
-    every shape and CTA size moves the same bytes."""
+    every shape, CTA size and scatter mode moves the same bytes."""
     g = TM_GEOS[geo]
-    knobs = {b"tm_tile_kib": tile_kib, b"tm_split_tile_kib": split_kib, b"tm_threads": threads}
+    knobs = {b"tm_tile_kib": tile_kib, b"tm_split_tile_kib": split_kib, b"tm_threads": threads,
+             b"tm_scatter_staged": staged}
     old = {k: native.bikv_get_tuning(k) for k in knobs}
     for k, v in knobs.items():
         assert native.bikv_set_tuning(k, v) == 0

@@ -9,7 +9,8 @@
 //                     ([slot][kv][head][dim])
 // Token-major pool of the reference (token = [dim][head][layer][kv]):
 //   k_token_major16v  2-byte elements: swizzled 16-byte shared-memory units,
-//                     cp.async double buffering on gather
+//                     cp.async double buffering of the pool rows (gather) or of
+//                     the worker vectors (scatter)
 //   k_token_major16   2-byte elements, any layer count: 4-byte units, odd pitch
 //   k_token_major<T>  1- and 4-byte elements
 // Flat reference copy:
@@ -746,6 +747,8 @@ __global__ void __launch_bounds__(256) k_token_major16(const __grid_constant__ T
 // lq -- the 8 lanes of a quarter warp have 8 consecutive hg, so the XOR sends them
 // to 8 different bank groups -- and turns the 8 x 4 (K,V) words into 4 K vectors and
 // 4 V vectors of 8 consecutive d, each part of a contiguous run of the warp.
+// The scatter stages the worker vectors instead (MODE 2 below) and keeps the tile form
+// (MODE 1) selectable for comparison.
 // ---------------------------------------------------------------------------
 struct TokenMajor16vArgs {
   const uint4* recs;

@@ -48,6 +48,19 @@ def test_tuning_knobs(native):
     native.bikv_set_tuning(b"bulk_stages", old)
 
 
+def test_every_knob_the_header_names_exists(native):
+    import os
+    import re
+    header = open(os.path.join(N.INCLUDE, "bikv.h")).read()
+    block = header[header.index("Tuning knobs:"):header.index("int bikv_set_tuning")]
+    names = re.findall(r'"([a-z0-9_]+)"', block)
+    assert len(names) >= 10
+    for name in names:
+        value = native.bikv_get_tuning(name.encode())
+        assert value >= 0, name
+        assert native.bikv_set_tuning(name.encode(), value) == 0, name
+
+
 def test_scratch_bytes(native):
     assert native.bikv_plan_scratch_bytes(0, 0) == 0
     assert native.bikv_plan_scratch_bytes(1, 1) == 512

@@ -29,6 +29,8 @@ std::atomic<long long> g_tm_max_groups{16};    // cap on d-groups per slab (k_to
 std::atomic<long long> g_tm_tile_kib{48};      // cap on one slab tile of k_token_major16v holding all heads, KiB
 std::atomic<long long> g_tm_split_tile_kib{96};  // the same for a slab that splits the heads
 std::atomic<long long> g_tm_scatter_staged{1};  // k_token_major16v scatter: 1 = through staged worker rows, 0 = through the transposed tile
+std::atomic<long long> g_tm_gather_stages{0};   // buffers in the gather's cp.async ring of k_token_major16v: 2, 3, 0 = by tile size
+std::atomic<long long> g_tm_scatter_stages{2};  // the same for the staged scatter
 std::atomic<long long> g_tm_max_heads{64};     // cap on heads per slab when the slab splits the heads
 
 int cuda_fail(cudaError_t e) {
@@ -219,8 +221,15 @@ int launch_token_major16v(const bikv_pool_desc* pool, const bikv_geometry* g, co
   const long long tile = per_gh * Hs * Gs;
   const bool staged = to_pool && g_tm_scatter_staged.load() != 0;
   const long long stage = 8ll * LU * ((Hs * Gs + 7u) & ~7u) * 16;   // the slab's worker vectors, unpadded
-  // the gather double-buffers the tile, the staged scatter the worker vectors
-  const long long smem = staged ? 2 * stage : (to_pool ? tile : 2 * tile);
+  // Ring depth: three buffers for tiles up to 48 KiB (gather at 28 layers: 0.92-0.93 of the HBM
+  // copy peak with 3 x 256 threads against 0.87-0.88 with 2 x 64); larger tiles keep two (three
+  // smaller ones measured 0.73-0.76 against 0.92 at 80 layers x 8 heads).
+  const long long unit = staged ? stage : tile;
+  long long stages = (to_pool ? g_tm_scatter_stages : g_tm_gather_stages).load();
+  if (stages == 0) stages = tile <= 48 * 1024 ? 3 : 2;
+  if (stages < 2) stages = 2;
+  if (stages * unit > di.max_optin_smem) stages = 2;
+  const long long smem = (to_pool && !staged) ? tile : stages * unit;
   if (smem > di.max_optin_smem) return 1;
   const unsigned slabs = (G / Gs) * (H / Hs);
   const long long items = n_pages * g->page_tokens * (long long)slabs;
@@ -263,8 +272,17 @@ int launch_token_major16v(const bikv_pool_desc* pool, const bikv_geometry* g, co
   const unsigned grid = (unsigned)std::min<long long>(items, (long long)di.sm_count * per_sm);
   if (grid == 0) return BIKV_OK;
   const int mode = staged ? 2 : (to_pool ? 1 : 0);
-  auto kern = Hs < H ? (mode == 2 ? k_token_major16v<true, 2> : mode == 1 ? k_token_major16v<true, 1> : k_token_major16v<true, 0>)
-                     : (mode == 2 ? k_token_major16v<false, 2> : mode == 1 ? k_token_major16v<false, 1> : k_token_major16v<false, 0>);
+  const bool ring3 = mode != 1 && stages == 3;
+  void (*kern)(TokenMajor16vArgs) = nullptr;
+  if (Hs < H) {
+    kern = mode == 1 ? k_token_major16v<true, 1, false>
+           : mode == 2 ? (ring3 ? k_token_major16v<true, 2, true> : k_token_major16v<true, 2, false>)
+                       : (ring3 ? k_token_major16v<true, 0, true> : k_token_major16v<true, 0, false>);
+  } else {
+    kern = mode == 1 ? k_token_major16v<false, 1, false>
+           : mode == 2 ? (ring3 ? k_token_major16v<false, 2, true> : k_token_major16v<false, 2, false>)
+                       : (ring3 ? k_token_major16v<false, 0, true> : k_token_major16v<false, 0, false>);
+  }
   BIKV_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)std::max<long long>(smem, 48 * 1024)));
   BIKV_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout,
@@ -276,7 +294,12 @@ int launch_token_major16v(const bikv_pool_desc* pool, const bikv_geometry* g, co
   // staged scatter 0.916 / 0.963 / 0.970 / 0.957 with 128 / 192 / 224 / 256; the scatter
   // through the transposed tile 0.753 / 0.766 / 0.786 with 128 / 192 / 256.
   unsigned threads = (unsigned)g_tm_threads.load();
-  if (threads == 0) threads = tile <= 48 * 1024 ? (to_pool && !staged ? 128 : 64) : (staged ? 224 : to_pool ? 256 : 192);
+  if (threads == 0) {
+    if (to_pool)
+      threads = staged ? (tile <= 48 * 1024 ? 64 : 224) : (tile <= 48 * 1024 ? 128 : 256);
+    else
+      threads = stages == 3 ? 256 : (tile <= 48 * 1024 ? 64 : 192);
+  }
   threads = std::min(256u, std::max(32u, threads & ~31u));
   kern<<<grid, threads, (size_t)smem, st>>>(a);
   return after_launch();
@@ -474,6 +497,8 @@ Knob* find_knob(const char* name) {
       {"tm_split_tile_kib", &g_tm_split_tile_kib, 8, 100},
       {"tm_max_heads", &g_tm_max_heads, 1, 64},
       {"tm_scatter_staged", &g_tm_scatter_staged, 0, 1},
+      {"tm_gather_stages", &g_tm_gather_stages, 0, 3},
+      {"tm_scatter_stages", &g_tm_scatter_stages, 0, 3},
   };
   if (!name) return nullptr;
   for (auto& k : knobs)

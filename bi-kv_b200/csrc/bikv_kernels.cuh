@@ -838,7 +838,8 @@ __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wai
 
 // SPLIT = the slab holds fewer heads than the pool row (Hs < H).  MODE: 0 = gather,
 // 1 = scatter through the transposed tile, 2 = scatter through staged worker rows.
-template <bool SPLIT, int MODE>
+// RING3: three buffers in the cp.async ring of modes 0 and 2 instead of two.
+template <bool SPLIT, int MODE, bool RING3>
 __global__ void __launch_bounds__(256) k_token_major16v(const __grid_constant__ TokenMajor16vArgs a) {
   extern __shared__ __align__(16) uint4 tm16v_tile[];
   const unsigned HG = a.Hs * a.Gs;
@@ -859,7 +860,60 @@ __global__ void __launch_bounds__(256) k_token_major16v(const __grid_constant__ 
         cp_async16(base + su * 16u, it.pool_p + pu);
       }
     };
+    auto emit = [&](const TmItem& cur, const uint4* tile) {
+      if (!cur.valid) return;
+      for (unsigned o = threadIdx.x; o < n_out; o += blockDim.x) {
+        const unsigned lq = a.div_HG.div(o);
+        const unsigned hg = o - lq * HG;
+        const unsigned h = a.div_Gs.div(hg);
+        const unsigned g = hg - h * a.Gs;
+        const unsigned q = lq ^ (hg & 7);
+        uint4 wv[8];
+#pragma unroll
+        for (unsigned j = 0; j < 8; ++j) wv[j] = tile[(((g << 3) + j) * a.Hs + h) * a.RU + q];
+        unsigned short* dst = cur.work_tok + (8ull * lq) * cur.plane_elems + h * a.D + g * 8;
+#pragma unroll
+        for (unsigned c = 0; c < 4; ++c) {
+          const unsigned x0 = (&wv[0].x)[c], x1 = (&wv[1].x)[c], x2 = (&wv[2].x)[c], x3 = (&wv[3].x)[c];
+          const unsigned x4 = (&wv[4].x)[c], x5 = (&wv[5].x)[c], x6 = (&wv[6].x)[c], x7 = (&wv[7].x)[c];
+          uint4 kv, vv;
+          kv.x = __byte_perm(x0, x1, 0x5410); vv.x = __byte_perm(x0, x1, 0x7632);
+          kv.y = __byte_perm(x2, x3, 0x5410); vv.y = __byte_perm(x2, x3, 0x7632);
+          kv.z = __byte_perm(x4, x5, 0x5410); vv.z = __byte_perm(x4, x5, 0x7632);
+          kv.w = __byte_perm(x6, x7, 0x5410); vv.w = __byte_perm(x6, x7, 0x7632);
+          st_stream16(dst + (2ull * c) * cur.plane_elems, kv);
+          st_stream16(dst + (2ull * c + 1) * cur.plane_elems, vv);
+        }
+      }
+    };
     unsigned w = blockIdx.x;
+    if constexpr (RING3) {
+      // Three tiles: the slabs of the next two items are in flight while the current one
+      // is transposed out.
+      TmItem cur = tm16v_item<SPLIT>(a, w);
+      TmItem nxt = tm16v_item<SPLIT>(a, w + gridDim.x);
+      load(cur, tm16v_tile);
+      cp_async_commit();
+      load(nxt, tm16v_tile + tile_units);
+      cp_async_commit();
+      unsigned buf = 0;
+      while (w < a.n_items) {
+        const TmItem after = tm16v_item<SPLIT>(a, w + 2 * gridDim.x);
+        const unsigned b2 = buf >= 1 ? buf - 1 : 2;   // (buf + 2) % 3
+        load(after, tm16v_tile + b2 * tile_units);
+        cp_async_commit();
+        asm volatile("cp.async.wait_group 2;" ::: "memory");
+        __syncthreads();
+        emit(cur, tm16v_tile + buf * tile_units);
+        __syncthreads();  // this tile is the target of the next iteration's load
+        cur = nxt;
+        nxt = after;
+        w += gridDim.x;
+        buf = buf == 2 ? 0 : buf + 1;
+      }
+      cp_async_wait_all();
+      return;
+    }
     TmItem cur = tm16v_item<SPLIT>(a, w);
     unsigned buf = 0;
     load(cur, tm16v_tile);
@@ -872,32 +926,7 @@ __global__ void __launch_bounds__(256) k_token_major16v(const __grid_constant__ 
       // everything but the group just committed has landed
       asm volatile("cp.async.wait_group 1;" ::: "memory");
       __syncthreads();
-      if (cur.valid) {
-        const uint4* tile = tm16v_tile + buf * tile_units;
-        for (unsigned o = threadIdx.x; o < n_out; o += blockDim.x) {
-          const unsigned lq = a.div_HG.div(o);
-          const unsigned hg = o - lq * HG;
-          const unsigned h = a.div_Gs.div(hg);
-          const unsigned g = hg - h * a.Gs;
-          const unsigned q = lq ^ (hg & 7);
-          uint4 wv[8];
-#pragma unroll
-          for (unsigned j = 0; j < 8; ++j) wv[j] = tile[(((g << 3) + j) * a.Hs + h) * a.RU + q];
-          unsigned short* dst = cur.work_tok + (8ull * lq) * cur.plane_elems + h * a.D + g * 8;
-#pragma unroll
-          for (unsigned c = 0; c < 4; ++c) {
-            const unsigned x0 = (&wv[0].x)[c], x1 = (&wv[1].x)[c], x2 = (&wv[2].x)[c], x3 = (&wv[3].x)[c];
-            const unsigned x4 = (&wv[4].x)[c], x5 = (&wv[5].x)[c], x6 = (&wv[6].x)[c], x7 = (&wv[7].x)[c];
-            uint4 kv, vv;
-            kv.x = __byte_perm(x0, x1, 0x5410); vv.x = __byte_perm(x0, x1, 0x7632);
-            kv.y = __byte_perm(x2, x3, 0x5410); vv.y = __byte_perm(x2, x3, 0x7632);
-            kv.z = __byte_perm(x4, x5, 0x5410); vv.z = __byte_perm(x4, x5, 0x7632);
-            kv.w = __byte_perm(x6, x7, 0x5410); vv.w = __byte_perm(x6, x7, 0x7632);
-            st_stream16(dst + (2ull * c) * cur.plane_elems, kv);
-            st_stream16(dst + (2ull * c + 1) * cur.plane_elems, vv);
-          }
-        }
-      }
+      emit(cur, tm16v_tile + buf * tile_units);
       __syncthreads();  // the tile may be overwritten by the load after next
       cur = nxt;
       w = w_next;
@@ -929,7 +958,62 @@ __global__ void __launch_bounds__(256) k_token_major16v(const __grid_constant__ 
         cp_async16(base + su * 16u, it.work_tok + (unsigned long long)p * it.plane_elems + h * a.D + g * 8);
       }
     };
+    auto emit = [&](const TmItem& cur, const uint4* stage) {
+      if (!cur.valid) return;
+      for (unsigned o = threadIdx.x; o < n_out; o += blockDim.x) {
+        const unsigned t = a.div_LU.div(o);
+        const unsigned lq = o - t * a.LU;
+        const unsigned g = a.div_Hs.div(t);
+        const unsigned h = t - g * a.Hs;
+        const unsigned hg = h * a.Gs + g;
+        const uint4* src = stage + (8 * lq) * HGp + (hg ^ (lq & 7));
+        uint4 kv[4], vv[4];
+#pragma unroll
+        for (unsigned c = 0; c < 4; ++c) {
+          kv[c] = src[(2 * c) * HGp];
+          vv[c] = src[(2 * c + 1) * HGp];
+        }
+        const unsigned row_pitch = a.H * a.LU;   // pool units between d and d + 1
+        uint4* dst = cur.pool_p + ((g << 3) * a.H + h) * a.LU + lq;
+#pragma unroll
+        for (unsigned j = 0; j < 8; ++j) {
+          // word c of row j: K_j of layer 4*lq + c in the low half, V_j in the high half
+          uint4 out;
+          const unsigned sel = (j & 1) ? 0x7632 : 0x5410;
+          out.x = __byte_perm((&kv[0].x)[j >> 1], (&vv[0].x)[j >> 1], sel);
+          out.y = __byte_perm((&kv[1].x)[j >> 1], (&vv[1].x)[j >> 1], sel);
+          out.z = __byte_perm((&kv[2].x)[j >> 1], (&vv[2].x)[j >> 1], sel);
+          out.w = __byte_perm((&kv[3].x)[j >> 1], (&vv[3].x)[j >> 1], sel);
+          st_stream16(dst + j * row_pitch, out);
+        }
+      }
+    };
     unsigned w = blockIdx.x;
+    if constexpr (RING3) {   // the worker vectors of the next two items in flight
+      TmItem cur = tm16v_item<SPLIT>(a, w);
+      TmItem nxt = tm16v_item<SPLIT>(a, w + gridDim.x);
+      load(cur, tm16v_tile);
+      cp_async_commit();
+      load(nxt, tm16v_tile + stage_units);
+      cp_async_commit();
+      unsigned buf = 0;
+      while (w < a.n_items) {
+        const TmItem after = tm16v_item<SPLIT>(a, w + 2 * gridDim.x);
+        const unsigned b2 = buf >= 1 ? buf - 1 : 2;   // (buf + 2) % 3
+        load(after, tm16v_tile + b2 * stage_units);
+        cp_async_commit();
+        asm volatile("cp.async.wait_group 2;" ::: "memory");
+        __syncthreads();
+        emit(cur, tm16v_tile + buf * stage_units);
+        __syncthreads();  // this stage is the target of the next iteration's load
+        cur = nxt;
+        nxt = after;
+        w += gridDim.x;
+        buf = buf == 2 ? 0 : buf + 1;
+      }
+      cp_async_wait_all();
+      return;
+    }
     TmItem cur = tm16v_item<SPLIT>(a, w);
     unsigned buf = 0;
     load(cur, tm16v_tile);
@@ -941,36 +1025,7 @@ __global__ void __launch_bounds__(256) k_token_major16v(const __grid_constant__ 
       cp_async_commit();
       asm volatile("cp.async.wait_group 1;" ::: "memory");
       __syncthreads();
-      if (cur.valid) {
-        const uint4* stage = tm16v_tile + buf * stage_units;
-        for (unsigned o = threadIdx.x; o < n_out; o += blockDim.x) {
-          const unsigned t = a.div_LU.div(o);
-          const unsigned lq = o - t * a.LU;
-          const unsigned g = a.div_Hs.div(t);
-          const unsigned h = t - g * a.Hs;
-          const unsigned hg = h * a.Gs + g;
-          const uint4* src = stage + (8 * lq) * HGp + (hg ^ (lq & 7));
-          uint4 kv[4], vv[4];
-#pragma unroll
-          for (unsigned c = 0; c < 4; ++c) {
-            kv[c] = src[(2 * c) * HGp];
-            vv[c] = src[(2 * c + 1) * HGp];
-          }
-          const unsigned row_pitch = a.H * a.LU;   // pool units between d and d + 1
-          uint4* dst = cur.pool_p + ((g << 3) * a.H + h) * a.LU + lq;
-#pragma unroll
-          for (unsigned j = 0; j < 8; ++j) {
-            // word c of row j: K_j of layer 4*lq + c in the low half, V_j in the high half
-            uint4 out;
-            const unsigned sel = (j & 1) ? 0x7632 : 0x5410;
-            out.x = __byte_perm((&kv[0].x)[j >> 1], (&vv[0].x)[j >> 1], sel);
-            out.y = __byte_perm((&kv[1].x)[j >> 1], (&vv[1].x)[j >> 1], sel);
-            out.z = __byte_perm((&kv[2].x)[j >> 1], (&vv[2].x)[j >> 1], sel);
-            out.w = __byte_perm((&kv[3].x)[j >> 1], (&vv[3].x)[j >> 1], sel);
-            st_stream16(dst + j * row_pitch, out);
-          }
-        }
-      }
+      emit(cur, tm16v_tile + buf * stage_units);
       __syncthreads();  // the stage may be overwritten by the load after next
       cur = nxt;
       w = w_next;

@@ -113,7 +113,9 @@ int bikv_last_cuda_error(void);
 int64_t bikv_launch_count(void);
 /* Tuning knobs: "ldst_ctas_per_sm", "bulk_ctas_per_sm", "bulk_stages",
  * "seg_bytes", "auto_variant", "ldst_threads", "tm_threads", "tm16_threads", "tm_max_groups",
- * "tm_tile_kib", "tm_split_tile_kib", "tm_max_heads", "tm_scatter_staged".  Returns BIKV_ERR_BAD_ARG for unknown names or values out of range. */
+ * "tm_tile_kib", "tm_split_tile_kib", "tm_max_heads", "tm_scatter_staged", "tm_gather_stages",
+ * "tm_scatter_stages".
+ * Returns BIKV_ERR_BAD_ARG for unknown names or values out of range. */
 int bikv_set_tuning(const char* name, int64_t value);
 int64_t bikv_get_tuning(const char* name);
 

@@ -122,7 +122,8 @@ def test_token_major_slab_shapes(cuda, native, geo, tile_kib, split_kib, threads
     every shape, CTA size and scatter mode moves the same bytes."""
     g = TM_GEOS[geo]
     knobs = {b"tm_tile_kib": tile_kib, b"tm_split_tile_kib": split_kib, b"tm_threads": threads,
-             b"tm_scatter_staged": staged}
+             b"tm_scatter_staged": staged, b"tm_gather_stages": 2 + staged,
+             b"tm_scatter_stages": 3 if threads in (0, 96) else 2}
     old = {k: native.bikv_get_tuning(k) for k in knobs}
     for k, v in knobs.items():
         assert native.bikv_set_tuning(k, v) == 0

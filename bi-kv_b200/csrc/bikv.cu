@@ -288,8 +288,8 @@ int launch_token_major16v(const bikv_pool_desc* pool, const bikv_geometry* g, co
   BIKV_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout,
                                  cudaSharedmemCarveoutMaxShared));
   // CTA size, by measurement (fractions of the HBM copy peak).  Tiles up to 48 KiB (28 layers,
-  // 2 or 4 heads): gather 0.87-0.88 with 64 threads, 0.85 with 96-128, 0.81 with 224-256;
-  // staged scatter 0.92-0.94 with 64, 0.90-0.91 with 96, 0.88-0.91 with 128, 0.77-0.80 with 32.
+  // 2 or 4 heads): gather with three tiles 0.92-0.93 with 256 threads, 0.90 with 128, 0.82-0.83
+  // with 64; with two tiles 0.87-0.88 with 64, 0.85 with 96-128, 0.81 with 224-256; staged scatter 0.92-0.94 with 64, 0.90-0.91 with 96, 0.88-0.91 with 128, 0.77-0.80 with 32.
   // 96 KiB tiles (80 layers x 8 heads): gather 0.912 / 0.923 / 0.916 with 128 / 192 / 256;
   // staged scatter 0.916 / 0.963 / 0.970 / 0.957 with 128 / 192 / 224 / 256; the scatter
   // through the transposed tile 0.753 / 0.766 / 0.786 with 128 / 192 / 256.

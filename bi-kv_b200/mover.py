@@ -76,17 +76,19 @@ class PageMover:
             buf = torch.empty((max(n, 64), 2), dtype=torch.int64).pin_memory()
         self._req_ring[slot] = [buf, None]
         self._req_slot = slot
-        tab = buf.numpy()
-        L, H, D = geom.n_layers, geom.n_kv_heads, geom.head_dim
+        head, tail = (geom.n_layers, 2), (geom.n_kv_heads, geom.head_dim)
+        rows = []
         for i, t in enumerate(ts):
-            if t.dim() != 5 or t.shape[0] != L or t.shape[1] != 2 or t.shape[3] != H or t.shape[4] != D:
-                raise ValueError(f"worker tensor {i} has shape {tuple(t.shape)}, want {geom.worker_shape('T')}")
-            if not t.is_contiguous() or t.element_size() != geom.elt_bytes:
+            sh = tuple(t.shape)
+            if len(sh) != 5 or sh[:2] != head or sh[3:] != tail:
+                raise ValueError(f"worker tensor {i} has shape {sh}, want {geom.worker_shape('T')}")
+            if t.element_size() != geom.elt_bytes or not t.is_contiguous():
                 raise ValueError(f"worker tensor {i} must be contiguous with {geom.elt_bytes}-byte elements")
             if t.device != self.device:
                 raise ValueError(f"worker tensor {i} lives on {t.device}, mover on {self.device}")
-            tab[i, 0] = t.data_ptr()
-            tab[i, 1] = t.shape[2]
+            rows.append((t.data_ptr(), sh[2]))
+        if rows:
+            buf.numpy()[:n] = rows
         return buf[:n]
 
     # -- host-plan path ----------------------------------------------------

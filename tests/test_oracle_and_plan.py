@@ -214,3 +214,18 @@ def test_table_views_outlive_their_plan(native):
     b = build_plan([[7, 8, 9]], [48], 16).table
     assert a.tolist() == [[1, 16, 0, 0], [2, 16, 0, 16], [3, 8, 0, 32]]
     assert b.tolist() == [[7, 16, 0, 0], [8, 16, 0, 16], [9, 16, 0, 32]]
+
+
+def test_page_lists_as_arrays_lists_and_mixed_flatten_alike():
+    rng = np.random.default_rng(3)
+    arrays = [rng.integers(0, 1000, size=n).astype(np.int32) for n in (5, 0, 17, 1)]
+    as_lists = [a.tolist() for a in arrays]
+    mixed = [arrays[0], as_lists[1], arrays[2].astype(np.int64), as_lists[3]]
+    want_flat = np.concatenate(arrays)
+    for form in (arrays, as_lists, mixed, [a.astype(np.int64) for a in arrays]):
+        flat, begin = flatten_page_lists(form)
+        assert flat.dtype == np.int32 and begin.dtype == np.int64
+        assert np.array_equal(flat, want_flat)
+        assert begin.tolist() == [0, 5, 5, 22, 23]
+    flat, begin = flatten_page_lists([])
+    assert len(flat) == 0 and begin.tolist() == [0]

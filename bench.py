@@ -29,9 +29,12 @@ sys.path.insert(0, ROOT)
 
 METRIC = "kv_page_gather_scatter_throughput"
 UNIT = "GB/s"
-# DRAM bytes per payload byte of one launch, from the ncu capture summarised under
-# profiles/k_paged_ldst_config1.md (small case, scaled by payload).
+# DRAM bytes (read + written) per payload byte of one k_paged_ldst launch, from an ncu capture
+# of `bench.py --small` (2,048-page pool, 8 requests, 1.38 GB payload); traffic grows in
+# proportion to the bytes copied, so the line scales it to the full launch and says so.
 NCU_TRAFFIC_PER_PAYLOAD_BYTE = 1.966
+NCU_TRAFFIC_SOURCE = "ncu --set full of k_paged_ldst on `bench.py --small` (1.38 GB payload), scaled by payload"
+NVLINK_NOMINAL_GBPS = 900.0     # per direction per GPU
 
 
 def parse_args():
@@ -73,7 +76,9 @@ def parse_args():
     ap.add_argument("--host-kv-steps", type=int, default=2,
                     help="N = 1: also time this many round trips with the worker KV tensors in pinned HOST memory "
                          "(the reference keeps its worker buffer on the CPU); 0 skips it")
-    ap.add_argument("--no-verify", action="store_true", help="skip the pool checksum before and after the run")
+    ap.add_argument("--no-sides", action="store_true",
+                    help="N = 1: skip the short side runs (token-major pools, paged worker KV) after the headline")
+    ap.add_argument("--no-verify", action="store_true", help="skip the closed-form check of one gather and one scatter and the pool hash before and after the run")
     return ap.parse_args()
 
 
@@ -166,8 +171,10 @@ def cpu_reference_run(steps, warmup, requests, limit_s=20.0):
     g = W.GEO_B
     pool_pages, sample_requests = 4096, min(8, requests)
     w = W.config1(seed=0, n_pages=pool_pages, n_requests=sample_requests)
-    plan = w.plan()
-    recs = plan.table.tolist()
+    # The plan comes from the oracle's own restatement of the reference's loop: this arm
+    # neither loads nor calls the CUDA library.
+    recs = O.plan_records([p.tolist() for p in w.page_lists], [int(t) for t in w.request_tokens], g.page_tokens,
+                          item_request=list(range(w.n_requests)))
     src, dst = O.token_indices(recs, g.page_tokens)
     gen = torch.Generator().manual_seed(0)
     # N(0,1) values; one token row drawn per page slot and repeated (a copy's speed does
@@ -197,7 +204,8 @@ def cpu_reference_run(steps, warmup, requests, limit_s=20.0):
               f"distribution on a {pool_pages}-page host pool, {done} round trips")
     return {"value": gbs, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port", "sample": sample,
             "ms_per_step": total / done * 1e3, "steps_done": done, "pages_per_s": 2 * w.n_pages * done / total,
-            "host_cpus": os.cpu_count()}
+            "host_cpus": os.cpu_count(), "pool_pages": pool_pages, "requests": sample_requests,
+            "pages_per_step": 2 * w.n_pages, "payload_bytes_per_direction": payload}
 
 
 def run_reference_arm(args, rank):
@@ -219,7 +227,13 @@ def run_reference_arm(args, rank):
         "impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": args.gpus,
         "steps": base["steps_done"], "warmup": args.warmup, "ms_per_step": base["ms_per_step"],
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u16", "data": "synthetic",
-        "config": config_dict(args, None),
+        "config": {"workload": "config1 geometry (28 layers, 4 KV heads, head 128, bf16, 16-token pages) on the "
+                               "host: token rows in CPU tensors, torch advanced indexing [BOUNDED SAMPLE of config1]",
+                   "sampled_from": "config1", "pool_pages": base["pool_pages"], "requests": base["requests"],
+                   "request_lengths": "lognormal(median 2048, sigma 0.8) clipped to [64, 8192]",
+                   "step": "gather all requests + scatter them back",
+                   "pages_per_step": base["pages_per_step"],
+                   "payload_bytes_per_direction": base["payload_bytes_per_direction"]},
         "cpu_baseline": {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")},
         "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0, "pages_per_s": base["pages_per_s"], "host_cpus": base["host_cpus"],
@@ -509,6 +523,120 @@ def run_config4(ctx):
     del shard
 
 
+# --------------------------------------------------------------------------- side measurements
+def peer_copy_ceilings(mover, pool, shard, rank, world, dev, barrier, total_bytes=2 << 30, reps=3):
+    """What a plain contiguous copy gets out of the links right now: every rank copies one
+    slice from (pull) or to (push) every peer's shard at the same time, the slices of a rank
+    on one stream per peer, once with the copy engines (cudaMemcpyAsync: independent of this
+    library's kernels) and once with the library's flat copy kernel.  GB/s per GPU, slowest
+    rank, best of `reps` after one untimed round.  Runs before the pool is filled: the pushed
+    slices overwrite the start of every shard."""
+    import torch
+    import torch.distributed as dist
+
+    peers = [r for r in range(world) if r != rank]
+    shard_bytes = shard.numel() * shard.element_size()
+    per = min(total_bytes // len(peers), shard_bytes // world) >> 20 << 20
+    if per <= 0:
+        return None
+    scratch = torch.empty(per * len(peers), dtype=torch.uint8, device=dev)
+    streams = [torch.cuda.Stream(dev) for _ in peers]
+    main = torch.cuda.current_stream(dev)
+
+    def run(copy, push):
+        times = []
+        for _ in range(reps + 1):
+            torch.cuda.synchronize()
+            barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(main)
+            for i, (st, p) in enumerate(zip(streams, peers)):
+                st.wait_event(e0)
+                remote, local = pool.bases[p] + rank * per, scratch.data_ptr() + i * per
+                copy(remote if push else local, local if push else remote, per, stream=st)
+                main.wait_stream(st)
+            e1.record(main)
+            main.synchronize()
+            times.append(e0.elapsed_time(e1))
+        t = torch.tensor([min(times[1:])], dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return per * len(peers) / (float(t[0]) / 1e3) / 1e9
+
+    out = {"engine_pull_GBps_per_gpu": run(mover.copy_range_engine, False),
+           "engine_push_GBps_per_gpu": run(mover.copy_range_engine, True),
+           "kernel_pull_GBps_per_gpu": run(mover.copy_range, False),
+           "kernel_push_GBps_per_gpu": run(mover.copy_range, True),
+           "bytes_per_gpu": per * len(peers),
+           "pattern": f"all {world} GPUs at once, each against its {len(peers)} peers, both link directions loaded; "
+                      "engine = cudaMemcpyAsync (copy engines), kernel = bikv_copy_range"}
+    torch.cuda.synchronize()
+    barrier()
+    del scratch
+    return out
+
+
+def side_measure(mover, dev, geom, pool_pages, n_requests, worker_layout, steps=5, warmup=3):
+    """One more (pool layout, worker layout) pair on this GPU, after the headline: gather and
+    scatter timed separately with CUDA events, the pool's position hash compared across the
+    round trips.  Fractions are of the measured HBM copy bandwidth, 2 x payload per launch."""
+    import numpy as np
+    import torch
+
+    import bikv_b200 as B
+    from bikv_b200 import selfcheck as S
+    from bikv_b200 import workloads as W
+    from bikv_b200.plan import build_block_plan
+
+    shard = B.ShardedPool.allocate_shard(geom, pool_pages, dev)
+    W.fill_normal_(shard, seed=4321)
+    pool = B.ShardedPool.single(shard, geom)
+    w = W.config1(seed=0, n_pages=pool_pages, n_requests=n_requests, geom=geom)
+    stream = torch.cuda.current_stream(dev)
+    if worker_layout == "nhd":
+        blocks = np.random.default_rng(7).permutation(w.n_pages)
+        plan = build_block_plan(w.flat(), w.request_tokens.astype("int32"), geom.page_tokens, blocks)
+        layers = [torch.zeros((w.n_pages * geom.page_tokens, 2, geom.n_kv_heads, geom.head_dim), dtype=geom.dtype,
+                              device=dev) for _ in range(geom.n_layers)]
+        gather = lambda: mover.gather_nhd(pool, plan, layers, validate=False)      # noqa: E731
+        scatter = lambda: mover.scatter_nhd(pool, plan, layers, validate=False)    # noqa: E731
+    else:
+        tensors = [torch.zeros(geom.worker_shape(int(t)), dtype=geom.dtype, device=dev) for t in w.request_tokens]
+        d_recs, d_reqs = mover.upload(w.plan(), geom, tensors)
+        gather = lambda: mover.gather_dev(pool, d_recs, d_reqs)                    # noqa: E731
+        scatter = lambda: mover.scatter_dev(pool, d_recs, d_reqs)                  # noqa: E731
+    before = S.position_hash(shard)
+    torch.cuda.synchronize()
+    torch.cuda.empty_cache()
+    for _ in range(warmup):
+        gather()
+        scatter()
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(steps)]
+    torch.cuda.synchronize()
+    for e in ev:
+        e[0].record(stream)
+        gather()
+        e[1].record(stream)
+        scatter()
+        e[2].record(stream)
+    torch.cuda.synchronize()
+    mover.check_status()
+    g_ms = statistics.mean(e[0].elapsed_time(e[1]) for e in ev)
+    s_ms = statistics.mean(e[1].elapsed_time(e[2]) for e in ev)
+    peak, peak_kind = measured_peaks()
+    same = S.position_hash(shard) == before
+    out = {"geometry": f"{geom.n_layers} layers x {geom.n_kv_heads} KV heads x {geom.head_dim}, {geom.elt_bytes}-byte "
+                       f"elements, {geom.page_tokens}-token pages",
+           "pool_pages": pool_pages, "requests": n_requests, "payload_bytes_per_direction": w.payload_bytes,
+           "gather_ms": g_ms, "scatter_ms": s_ms,
+           "gather_frac": 2 * w.payload_bytes / (g_ms / 1e3) / 1e9 / peak,
+           "scatter_frac": 2 * w.payload_bytes / (s_ms / 1e3) / 1e9 / peak,
+           "value_GBps": 2 * w.payload_bytes / ((g_ms + s_ms) / 1e3) / 1e9, "peak_kind": f"of {peak_kind}",
+           "steps": steps, "pool_hash_unchanged": same}
+    if not same:
+        raise SystemExit("bench.py: a side measurement changed its pool across round trips")
+    return out
+
+
 # --------------------------------------------------------------------------- GPU arm
 def main():
     args = parse_args()
@@ -570,7 +698,6 @@ def main():
     if args.layout == "token_major":
         geom = geom.with_layout(N.POOL_TOKEN_MAJOR)
     shard = B.ShardedPool.allocate_shard(geom, args.pool_pages, dev)
-    W.fill_normal_(shard, seed=1234 + rank)
     if multi:
         pool = B.ShardedPool.exchange(shard, geom, group=cpu_group)
         all_w = [W.config2(r, world, seed=0, pages_per_shard=args.pool_pages, n_requests=args.requests, geom=geom,
@@ -654,6 +781,50 @@ def main():
         if multi:
             dist.barrier(group=cpu_group)
 
+    def all_ranks_agree(flag):
+        if not multi:
+            return bool(flag)
+        t_ok = torch.tensor([float(bool(flag))], dtype=torch.float64)
+        dist.all_reduce(t_ok, op=dist.ReduceOp.MIN)
+        return bool(t_ok[0])
+
+    # ---- what the links give a plain contiguous copy (before the pool holds anything) ----
+    peer_copy = peer_copy_ceilings(mover, pool, shard, rank, world, dev, barrier) if multi else None
+
+    # ---- content-addressed check of the launches that are timed below ----
+    closed_form = {"gather_closed_form": None, "scatter_closed_form": None}
+    if not args.no_verify and args.layout == "paged" and not nhd and args.only == "both":
+        from bikv_b200 import selfcheck as S
+        ids = S.global_ids_of_shard(rank, world, args.pool_pages)
+        S.fill_pool_(shard, geom, ids)
+        torch.cuda.synchronize()
+        barrier()
+        launch_gather()
+        stream.synchronize()
+        barrier()
+        ok_g = all(S.check_gathered(geom, t, pl, int(n)) for t, pl, n in zip(tensors, w.page_lists, w.request_tokens))
+        for r, t in enumerate(tensors):
+            S.fill_worker_(geom, t, rank, r)
+        torch.cuda.synchronize()
+        barrier()
+        launch_scatter()
+        stream.synchronize()
+        barrier()
+        touched = S.touched_pages(all_w if multi else [w], rank, world, args.pool_pages)
+        ok_s = S.check_scattered_pool(shard, geom, ids, touched)
+        mover.check_status()
+        closed_form = {"gather_closed_form": all_ranks_agree(ok_g), "scatter_closed_form": all_ranks_agree(ok_s)}
+        if not (closed_form["gather_closed_form"] and closed_form["scatter_closed_form"]):
+            if rank == 0:
+                print(json.dumps({"metric": METRIC, "n_gpus": world, "verified": closed_form,
+                                  "error": "closed-form check failed"}), flush=True)
+            raise SystemExit("bench.py: gathered or scattered words differ from what the plan implies")
+        for t in tensors:
+            t.zero_()
+    W.fill_normal_(shard, seed=1234 + rank)
+    torch.cuda.synchronize()
+    barrier()
+
     do_g, do_s = args.only in ("both", "gather"), args.only in ("both", "scatter")
     n_dirs = int(do_g) + int(do_s)
 
@@ -694,15 +865,12 @@ def main():
         mover.check_status()          # 16-byte device->host read, synchronises the step
 
     def shard_checksum():
-        """Bit-level checksum of this rank's shard.  A step scatters back exactly what it
-        gathered, so the pool must come out of the whole run unchanged (checked after the
-        timed regions, on every rank, at full size)."""
-        words = shard.view(-1).view(torch.int32)          # every geometry's page is a multiple of 4 bytes
-        total = torch.zeros((), dtype=torch.int64, device=dev)
-        step = 1 << 27                                     # 1 GiB of int64 scratch per chunk
-        for at in range(0, words.numel(), step):
-            total += words[at:at + step].sum(dtype=torch.int64)
-        return int(total)
+        """Position-weighted hash of this rank's shard (every 32-bit word weighted by a hash of
+        its index, so words that move change it).  A step scatters back exactly what it gathered,
+        so the pool must come out of the whole run unchanged (checked after the timed regions,
+        on every rank, at full size)."""
+        from bikv_b200 import selfcheck as S
+        return S.position_hash(shard)
 
     checksum_before = shard_checksum() if args.only == "both" and not args.no_verify else None
     # Give back the scratch blocks that filling and checksumming the pool left in torch's
@@ -800,15 +968,24 @@ def main():
                            "(the reference keeps its worker buffer on the CPU, Worker/Worker.py:57-62)"}
         del host
 
+    # ---- the reference's own pool layout and the worker's paged KV, one short run each ----
+    sides = None
+    if not multi and not args.no_sides and args.workload == "auto" and args.geometry == "B" and \
+            args.layout == "paged" and not nhd and args.only == "both" and not args.small:
+        geo_r = B.KVGeometry(28, 2, 128, 16, torch.float16, N.POOL_TOKEN_MAJOR)
+        sides = {
+            "token_major_pool_reference_geometry": dict(side_measure(mover, dev, geo_r, 16384, 64, "contiguous"),
+                                                        kernel="k_token_major16v"),
+            "token_major_pool_config1_geometry": dict(side_measure(mover, dev, W.GEO_B.with_layout(N.POOL_TOKEN_MAJOR),
+                                                                   16384, 64, "contiguous"), kernel="k_token_major16v"),
+            "paged_pool_to_paged_worker_kv": dict(side_measure(mover, dev, W.GEO_B, 16384, 64, "nhd"),
+                                                  kernel="k_paged_nhd"),
+        }
+
     verified = None
     if checksum_before is not None:
         barrier()
-        ok = float(shard_checksum() == checksum_before)
-        if multi:
-            t_ok = torch.tensor([ok], dtype=torch.float64)
-            dist.all_reduce(t_ok, op=dist.ReduceOp.MIN)
-            ok = float(t_ok[0])
-        verified = bool(ok)
+        verified = all_ranks_agree(shard_checksum() == checksum_before)
         if not verified:
             raise SystemExit("bench.py: the pool changed across gather->scatter round trips (bits differ)")
 
@@ -843,7 +1020,8 @@ def main():
             kernel = "k_paged_nhd"
         roofline = {
             "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-            "traffic": None if NCU_TRAFFIC_PER_PAYLOAD_BYTE is None else NCU_TRAFFIC_PER_PAYLOAD_BYTE * payload,
+            "traffic": NCU_TRAFFIC_PER_PAYLOAD_BYTE * payload if kernel == "k_paged_ldst" else None,
+            "traffic_source": NCU_TRAFFIC_SOURCE if kernel == "k_paged_ldst" else None,
             "peak_kind": f"of {peak_kind}", "kernel": kernel,
             "algorithmic_bytes_per_launch": 2 * payload, "launch_ms": launch_ms,
             "gather_ms": statistics.mean(gather_ms), "scatter_ms": statistics.mean(scatter_ms),
@@ -857,10 +1035,12 @@ def main():
                 nv = pushed_remote_bytes / (statistics.mean(gather_ms) / 1e3) / 1e9
             out_gbps = remote * payload / (statistics.mean(scatter_ms) / 1e3) / 1e9
             # With (N-1)/N of the pages remote the launches are NVLink-bound, not HBM-bound: the
-            # roofline is remote bytes per GPU against the measured peer-copy bandwidth (770 GB/s
-            # per direction on this pool; 900 nominal).  The HBM view stays in "hbm".
-            roofline = {"bound": "nvlink", "achieved": (nv + out_gbps) / 2, "peak": 770.0, "unit": "GB/s",
-                        "frac": (nv + out_gbps) / 2 / 770.0, "traffic": None, "peak_kind": "of measured peer copy",
+            # roofline is remote bytes per GPU against the link's nominal rate per direction; what
+            # contiguous copies reached on these GPUs a moment ago stands beside it.  The HBM view
+            # stays in "hbm".
+            roofline = {"bound": "nvlink", "achieved": (nv + out_gbps) / 2, "peak": NVLINK_NOMINAL_GBPS, "unit": "GB/s",
+                        "frac": (nv + out_gbps) / 2 / NVLINK_NOMINAL_GBPS, "traffic": None,
+                        "peak_kind": "of nominal NVLink 5 (900 GB/s per direction per GPU)",
                         "kernel": kernel, "algorithmic_bytes_per_launch": remote * payload,
                         "launch_ms": launch_ms, "gather_ms": statistics.mean(gather_ms),
                         "scatter_ms": statistics.mean(scatter_ms),
@@ -868,16 +1048,22 @@ def main():
                                 "gather (ingress) and scatter (egress) launches",
                         "hbm": roofline}
             roofline["nvlink"] = {"remote_fraction": remote, "gather_mode": args.gather_mode,
-                                  "gather_ingress_GBps_per_gpu": nv,
-                                  "frac_of_770_measured": nv / 770.0, "frac_of_900_nominal": nv / 900.0,
-                                  "scatter_egress_GBps_per_gpu": remote * payload / (statistics.mean(scatter_ms) / 1e3) / 1e9}
+                                  "gather_ingress_GBps_per_gpu": nv, "gather_frac_of_900_nominal": nv / NVLINK_NOMINAL_GBPS,
+                                  "scatter_egress_GBps_per_gpu": out_gbps,
+                                  "scatter_frac_of_900_nominal": out_gbps / NVLINK_NOMINAL_GBPS,
+                                  "peer_copy_measured_in_this_run": peer_copy}
+            if peer_copy:
+                best_in = max(peer_copy["engine_pull_GBps_per_gpu"], peer_copy["kernel_pull_GBps_per_gpu"],
+                              peer_copy["engine_push_GBps_per_gpu"], peer_copy["kernel_push_GBps_per_gpu"])
+                roofline["nvlink"]["gather_frac_of_best_contiguous_copy"] = nv / best_in
+                roofline["nvlink"]["scatter_frac_of_best_contiguous_copy"] = out_gbps / best_in
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "u16", "data": "synthetic",
             "config": config_dict(args, w), "pages_per_s": n_dirs * total_pages * args.steps / secs,
             "roofline": roofline, "gpu_launches": total_launches, "clocks": clocks,
-            "verified": {"pool_unchanged_after_round_trips": verified},
+            "verified": dict(closed_form, pool_hash_unchanged=verified),
         }
         if e2e:
             line["e2e"] = {"value": n_dirs * total_payload * args.steps / e2e["seconds"] / 1e9, "unit": UNIT,
@@ -888,6 +1074,8 @@ def main():
                                    "plan in pinned host memory; the pool and the worker KV tensors stay in HBM"}
         if host_kv:
             line["e2e_host_kv"] = host_kv
+        if sides:
+            line["side_measurements"] = sides
         if not multi and not args.no_cpu_baseline:
             base = cpu_reference_run(20, 1, args.requests, limit_s=15.0)
             line["cpu_baseline"] = {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")}

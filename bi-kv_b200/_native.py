@@ -95,6 +95,7 @@ SIGNATURES = {
         C.c_int,
         [_P, C.c_int64, _P, C.c_int32, C.POINTER(PoolDesc), C.POINTER(Geometry), C.c_int],
     ),
+    "bikv_check_worker_base": (C.c_int, [_P]),
     "bikv_gather": (
         C.c_int,
         [C.POINTER(PoolDesc), C.POINTER(Geometry), _P, C.c_int64, _P, C.c_int32, C.c_int, _P, _P],
@@ -123,6 +124,7 @@ SIGNATURES = {
     ),
     "bikv_copy_pages_flat": (C.c_int, [_P, _P, _P, _P, C.c_int64, C.c_int64, C.c_int32, _P]),
     "bikv_copy_range": (C.c_int, [_P, _P, C.c_int64, _P]),
+    "bikv_copy_range_engine": (C.c_int, [_P, _P, C.c_int64, _P]),
     "bikv_selftest_wait_timeout": (C.c_int, [_P, C.c_int64, _P]),
     "bikv_can_access_peer": (C.c_int, [C.c_int, C.c_int, C.POINTER(C.c_int)]),
     "bikv_enable_peer": (C.c_int, [C.c_int, C.c_int]),

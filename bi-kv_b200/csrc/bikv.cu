@@ -21,6 +21,7 @@ std::atomic<long long> g_ldst_ctas_per_sm{16};
 std::atomic<long long> g_bulk_ctas_per_sm{3};
 std::atomic<long long> g_bulk_stages{4};
 std::atomic<long long> g_seg_bytes{16384};
+std::atomic<long long> g_bulk_span{1};     // adjacent planes of a page per stage of the bulk ring
 std::atomic<long long> g_auto_variant{0};  // 0 = choose by shard count
 std::atomic<long long> g_tm_threads{0};        // CTA size of k_token_major16v; 0 = by tile size (see launcher)
 std::atomic<long long> g_ldst_threads{256};    // CTA size of k_paged_ldst (k_paged_nhd and k_flat use 256)
@@ -420,12 +421,20 @@ int launch_paged(const bikv_pool_desc* pool, const bikv_geometry* g, const bikv_
   }
   int stages = (int)g_bulk_stages.load();
   long long per_sm = g_bulk_ctas_per_sm.load();
+  // Adjacent planes per ring stage ("bulk_span").  Only when a stage holds whole planes.
+  unsigned span = (unsigned)g_bulk_span.load();
+  if (a.parts != 1 || span > a.planes) span = a.parts != 1 ? 1u : a.planes;
   const long long budget = std::min<long long>(di.max_optin_smem, 227 * 1024) - 1024;
-  while (stages > 2 && (long long)stages * seg > budget) --stages;
-  if ((long long)stages * seg > budget) return BIKV_ERR_TOO_LARGE;
-  const long long smem = (long long)stages * seg;
+  while (span > 1 && 2ll * seg * span > budget) --span;   // at least two stages must fit
+  a.span = span;
+  a.groups = (a.planes + span - 1) / span;
+  if (span > 1) a.n_items = (unsigned)(n_pages * (long long)a.groups);   // fewer than `items`, which fitted
+  const long long stage_bytes = (long long)seg * span;
+  while (stages > 2 && (long long)stages * stage_bytes > budget) --stages;
+  if ((long long)stages * stage_bytes > budget) return BIKV_ERR_TOO_LARGE;
+  const long long smem = (long long)stages * stage_bytes;
   while (per_sm > 1 && per_sm * (smem + 1024) > 227 * 1024) --per_sm;
-  unsigned grid = (unsigned)std::min<long long>(items, (long long)di.sm_count * per_sm);
+  unsigned grid = (unsigned)std::min<long long>(a.n_items, (long long)di.sm_count * per_sm);
   // The kernel also holds a few static bytes (its mbarriers), so opt in well
   // before the 48 KiB default limit.
   if (smem > 40 * 1024)
@@ -488,6 +497,7 @@ Knob* find_knob(const char* name) {
       {"bulk_ctas_per_sm", &g_bulk_ctas_per_sm, 1, 16},
       {"bulk_stages", &g_bulk_stages, 2, kMaxStages},
       {"seg_bytes", &g_seg_bytes, 1024, 64 * 1024},
+      {"bulk_span", &g_bulk_span, 1, 8},
       {"auto_variant", &g_auto_variant, 0, BIKV_VARIANT_BULK},
       {"ldst_threads", &g_ldst_threads, 64, 256},
       {"tm_threads", &g_tm_threads, 0, 256},
@@ -587,6 +597,10 @@ int64_t bikv_plan_build(const int32_t* pages_flat, const int64_t* item_page_begi
   return n;
 }
 
+int bikv_check_worker_base(const void* base) {
+  return worker_base_status((unsigned long long)(uintptr_t)base);
+}
+
 int bikv_plan_validate(const bikv_page_rec* recs, int64_t n_pages, const bikv_request_desc* requests,
                        int32_t n_requests, const bikv_pool_desc* pool, const bikv_geometry* geom,
                        int check_overlap) {
@@ -600,7 +614,8 @@ int bikv_plan_validate(const bikv_page_rec* recs, int64_t n_pages, const bikv_re
   const int64_t total_pages = pool->pages_per_shard * pool->n_shards;
   for (int32_t r = 0; r < n_requests; ++r) {
     if (requests[r].tokens < 0) return BIKV_ERR_BAD_ARG;
-    if (requests[r].base && (((uintptr_t)requests[r].base) & 15)) return BIKV_ERR_ALIGNMENT;
+    if (requests[r].base && worker_base_status((unsigned long long)(uintptr_t)requests[r].base))
+      return BIKV_ERR_ALIGNMENT;
   }
   for (int64_t i = 0; i < n_pages; ++i) {
     const bikv_page_rec& p = recs[i];
@@ -780,6 +795,14 @@ int bikv_copy_range(void* dst, const void* src, int64_t bytes, void* stream) {
   return bikv_copy_pages_flat(src, dst, nullptr, nullptr, 1, bytes, 1, stream);
 }
 
+int bikv_copy_range_engine(void* dst, const void* src, int64_t bytes, void* stream) {
+  if (bytes < 0) return BIKV_ERR_BAD_ARG;
+  if (bytes == 0) return BIKV_OK;
+  if (!dst || !src) return BIKV_ERR_BAD_ARG;
+  BIKV_CUDA(cudaMemcpyAsync(dst, src, (size_t)bytes, cudaMemcpyDefault, (cudaStream_t)stream));
+  return BIKV_OK;
+}
+
 int bikv_can_access_peer(int device, int peer, int* can) {
   if (!can) return BIKV_ERR_BAD_ARG;
   if (device == peer) {
@@ -902,17 +925,19 @@ extern "C" int bikv_gather_h_static(const bikv_pool_desc* pool, const bikv_geome
                                     int validate, int variant, int32_t* status_dev, void* stream) {
   if (n_pages < 0 || n_requests < 0) return BIKV_ERR_BAD_ARG;
   if (n_pages > BIKV_STATIC_MAX_PAGES || n_requests > BIKV_STATIC_MAX_REQUESTS) return BIKV_ERR_TOO_LARGE;
+  // Looked up before the empty-plan return, so that a call with n_pages == 0 serves as the
+  // start-up call that places the array on the device.
+  unsigned char* scratch = nullptr;
+  int rc = static_plan_address(&scratch);
+  if (rc) return rc;
   if (n_pages == 0) return BIKV_OK;
   if (!recs_host || !requests_host || n_requests == 0) return BIKV_ERR_BAD_ARG;
   for (int32_t r = 0; r < n_requests; ++r)
     if (!requests_host[r].base) return BIKV_ERR_BAD_ARG;
   if (validate) {
-    int rc = bikv_plan_validate(recs_host, n_pages, requests_host, n_requests, pool, geom, 0);
+    rc = bikv_plan_validate(recs_host, n_pages, requests_host, n_requests, pool, geom, 0);
     if (rc) return rc;
   }
-  unsigned char* scratch = nullptr;
-  int rc = static_plan_address(&scratch);
-  if (rc) return rc;
   // Records at the front, request table behind the record area's full extent.
   unsigned char* d_recs = scratch;
   unsigned char* d_reqs = scratch + (size_t)BIKV_STATIC_MAX_PAGES * sizeof(bikv_page_rec);

@@ -49,6 +49,8 @@ struct PagedArgs {
   unsigned n_requests;             // bounds for the record checks below
   unsigned page_tokens;
   unsigned long long total_pages;  // n_shards * pages_per_shard
+  unsigned span;                   // bulk ring: adjacent planes per item (1 = one plane or part)
+  unsigned groups;                 // ceil(planes / span)
 };
 
 // A record that points outside the pool or outside its worker tensor is skipped, never
@@ -72,12 +74,26 @@ __device__ __forceinline__ bool record_ok(const uint4& r, unsigned n_requests, u
   if (status) atomicCAS(status, 0, err);
   return false;
 }
-__device__ __forceinline__ bool window_ok(const uint4& r, long long tensor_tokens, int* status) {
+// The one rule for a worker-side base address (a request's KV tensor, a layer tensor of a
+// paged worker cache): not null and 16-byte aligned, because bulk copies, cp.async and the
+// vector loads and stores are issued on addresses derived from it.  Host validation and
+// every kernel use this same function.
+__host__ __device__ __forceinline__ int worker_base_status(unsigned long long base) {
+  if (base == 0) return BIKV_ERR_BAD_ARG;
+  if (base & 15ull) return BIKV_ERR_ALIGNMENT;
+  return BIKV_OK;
+}
+// Checks the request descriptor a record selected: its base address and that the record's
+// token window lies inside the tensor.  Called before any address is formed from `base`.
+__device__ __forceinline__ bool window_ok(const uint4& r, unsigned long long base, long long tensor_tokens,
+                                          int* status) {
 #ifdef BIKV_NO_RECORD_CHECKS
   return true;
 #endif
-  if ((long long)r.w + (long long)r.y <= tensor_tokens) return true;
-  if (status) atomicCAS(status, 0, (int)BIKV_ERR_DST_RANGE);
+  int err = worker_base_status(base);
+  if (err == 0 && (long long)r.w + (long long)r.y > tensor_tokens) err = BIKV_ERR_DST_RANGE;
+  if (err == 0) return true;
+  if (status) atomicCAS(status, 0, err);
   return false;
 }
 
@@ -120,7 +136,7 @@ __device__ __forceinline__ bool decode_item(const PagedArgs& a, unsigned w, char
   }
   pool_p = a.pool.base[shard] + local * a.page_bytes + (unsigned long long)plane * a.plane_bytes + off;
   const longlong2 rq = __ldg(reinterpret_cast<const longlong2*>(a.reqs + r.z));
-  if (!window_ok(r, rq.y, a.status)) return false;
+  if (!window_ok(r, (unsigned long long)rq.x, rq.y, a.status)) return false;
   work_p = reinterpret_cast<char*>(rq.x) +
            ((unsigned long long)plane * (unsigned long long)rq.y + r.w) * a.row_bytes + off;
   return true;
@@ -231,7 +247,11 @@ __global__ void __launch_bounds__(256) k_paged_nhd(const __grid_constant__ NhdAr
     const unsigned page = w / a.planes;
     uint4 r = __ldg(a.recs + page);
     r.z = 0;  // the request field is unused for a paged worker cache
-    if (!record_ok(r, 1, a.page_tokens, a.total_pages, a.status) || !window_ok(r, a.slots_per_layer, a.status))
+    // The layer table lives in device memory like the records: its entry is checked (not
+    // null, 16-byte aligned) together with the slot window, before any address is formed.
+    const unsigned long long layer_addr = __ldg(reinterpret_cast<const unsigned long long*>(a.layer_bases) + (plane >> 1));
+    if (!record_ok(r, 1, a.page_tokens, a.total_pages, a.status) ||
+        !window_ok(r, layer_addr, a.slots_per_layer, a.status))
       continue;
     const unsigned id = r.x;
     unsigned shard;
@@ -245,9 +265,8 @@ __global__ void __launch_bounds__(256) k_paged_nhd(const __grid_constant__ NhdAr
     }
     uint4* pool_p = reinterpret_cast<uint4*>(a.pool.base[shard] + local * a.page_bytes +
                                              (unsigned long long)plane * a.plane_bytes);
-    const unsigned layer = plane >> 1, kv = plane & 1;
-    char* layer_base = reinterpret_cast<char*>(
-        __ldg(reinterpret_cast<const unsigned long long*>(a.layer_bases) + layer));
+    const unsigned kv = plane & 1;
+    char* layer_base = reinterpret_cast<char*>(layer_addr);
     uint4* work_p = reinterpret_cast<uint4*>(layer_base + ((unsigned long long)r.w * 2 + kv) * a.row_bytes);
     const unsigned n = r.y * a.row_vecs;
     auto wi = [&](unsigned i) {   // worker-side vector index of pool-side vector i
@@ -343,6 +362,54 @@ __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wa
 
 constexpr int kMaxStages = 12;
 
+// One stage of the bulk ring: `np` adjacent planes of one page (np = 1 with `vbytes` the size
+// of a part of a plane when planes are split, or when span is 1).  Pool side: the planes
+// are adjacent, plane_bytes apart; worker side: `work_stride` apart.
+struct BulkItem {
+  char* pool_p;
+  char* work_p;
+  unsigned long long work_stride;
+  unsigned vbytes;   // valid bytes of each plane (or of the part)
+  unsigned np;       // planes in this item; 0 = nothing to copy
+};
+
+// Resolves item w of a launch whose items are (page, group of `span` adjacent planes).
+__device__ __forceinline__ BulkItem decode_span(const PagedArgs& a, unsigned w) {
+  BulkItem it;
+  it.np = 0;
+  if (a.span <= 1) {
+    unsigned bytes;
+    if (!decode_item(a, w, it.pool_p, it.work_p, bytes)) return it;
+    it.work_stride = 0;
+    it.vbytes = bytes;
+    it.np = 1;
+    return it;
+  }
+  const unsigned group = w % a.groups;
+  const unsigned page = w / a.groups;
+  const uint4 r = __ldg(a.recs + page);
+  if (!record_ok(r, a.n_requests, a.page_tokens, a.total_pages, a.status)) return it;
+  const unsigned plane0 = group * a.span;
+  const unsigned id = r.x;
+  unsigned shard;
+  unsigned long long local;
+  if (a.pool.rule == BIKV_SHARD_MOD) {
+    shard = id % (unsigned)a.pool.n_shards;
+    local = id / (unsigned)a.pool.n_shards;
+  } else {
+    shard = (unsigned)(id / a.pool.pages_per_shard);
+    local = id % a.pool.pages_per_shard;
+  }
+  const longlong2 rq = __ldg(reinterpret_cast<const longlong2*>(a.reqs + r.z));
+  if (!window_ok(r, (unsigned long long)rq.x, rq.y, a.status)) return it;
+  it.pool_p = a.pool.base[shard] + local * a.page_bytes + (unsigned long long)plane0 * a.plane_bytes;
+  it.work_stride = (unsigned long long)rq.y * a.row_bytes;
+  it.work_p = reinterpret_cast<char*>(rq.x) + plane0 * it.work_stride + (unsigned long long)r.w * a.row_bytes;
+  it.vbytes = r.y * a.row_bytes;
+  it.np = min(a.span, a.planes - plane0);
+  return it;
+}
+
 __global__ void __launch_bounds__(32) k_paged_bulk(const __grid_constant__ PagedArgs a, int stages) {
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ __align__(8) unsigned long long bars[kMaxStages];
@@ -353,30 +420,39 @@ __global__ void __launch_bounds__(32) k_paged_bulk(const __grid_constant__ Paged
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 
   const uint32_t buf0 = smem_u32(smem);
+  const unsigned stage_bytes = a.seg_bytes * (a.span ? a.span : 1u);
   const unsigned stride = gridDim.x;
-  // Number of chunks this CTA owns: w = blockIdx.x + k*stride.
+  // Number of items this CTA owns: w = blockIdx.x + k*stride.
   const unsigned mine = (a.n_items > blockIdx.x) ? (a.n_items - blockIdx.x + stride - 1) / stride : 0;
 
   unsigned phase_bits = 0;      // bit s = parity to wait for on stage s
   unsigned loaded_bits = 0;     // bit s = a load is outstanding on stage s
-  // Per-stage destination and size of the chunk held there.
-  char* st_dst[kMaxStages];
-  unsigned st_bytes[kMaxStages];
+  BulkItem st[kMaxStages];      // the item held in each stage
   bool failed = false;
 
+  // Gather: the planes of a pool page are adjacent, so ONE bulk load brings all of the
+  // item's planes (up to the valid rows of the last one); each plane then leaves with its
+  // own bulk store into its window of the worker tensor.  Scatter: one bulk load per
+  // plane window, all counted on the stage's barrier; a full page's planes leave with one
+  // store, a partial page's with one store per plane.
   auto issue_load = [&](unsigned k) {
     const int s = k % stages;
-    char *pool_p, *work_p;
-    unsigned bytes;
-    st_bytes[s] = 0;
+    st[s].np = 0;
     if (k >= mine) return;
-    if (!decode_item(a, blockIdx.x + k * stride, pool_p, work_p, bytes)) return;
-    const char* src = a.to_pool ? work_p : pool_p;
-    st_dst[s] = a.to_pool ? pool_p : work_p;
-    st_bytes[s] = bytes;
+    st[s] = decode_span(a, blockIdx.x + k * stride);
+    const BulkItem& it = st[s];
+    if (it.np == 0) return;
     const uint32_t bar = smem_u32(&bars[s]);
-    mbar_expect_tx(bar, bytes);
-    bulk_g2s(buf0 + s * a.seg_bytes, src, bytes, bar);
+    const uint32_t buf = buf0 + s * stage_bytes;
+    if (!a.to_pool) {
+      const unsigned bytes = (it.np - 1) * a.plane_bytes + it.vbytes;
+      mbar_expect_tx(bar, bytes);
+      bulk_g2s(buf, it.pool_p, bytes, bar);
+    } else {
+      mbar_expect_tx(bar, it.np * it.vbytes);
+      for (unsigned p = 0; p < it.np; ++p)
+        bulk_g2s(buf + p * a.plane_bytes, it.work_p + p * it.work_stride, it.vbytes, bar);
+    }
     loaded_bits |= 1u << s;
   };
 
@@ -384,19 +460,29 @@ __global__ void __launch_bounds__(32) k_paged_bulk(const __grid_constant__ Paged
 
   for (unsigned k = 0; k < mine; ++k) {
     const int s = k % stages;
-    if (st_bytes[s] != 0) {
+    const BulkItem& it = st[s];
+    if (it.np != 0) {
       if (!mbar_wait_bounded(smem_u32(&bars[s]), (phase_bits >> s) & 1)) {
         failed = true;
         break;
       }
       phase_bits ^= 1u << s;
       loaded_bits &= ~(1u << s);
-      bulk_s2g(st_dst[s], buf0 + s * a.seg_bytes, st_bytes[s]);
+      const uint32_t buf = buf0 + s * stage_bytes;
+      if (!a.to_pool) {
+        for (unsigned p = 0; p < it.np; ++p)
+          bulk_s2g(it.work_p + p * it.work_stride, buf + p * a.plane_bytes, it.vbytes);
+      } else if (it.np == 1 || it.vbytes == a.plane_bytes) {
+        bulk_s2g(it.pool_p, buf, (it.np - 1) * a.plane_bytes + it.vbytes);
+      } else {
+        for (unsigned p = 0; p < it.np; ++p)
+          bulk_s2g(it.pool_p + (unsigned long long)p * a.plane_bytes, buf + p * a.plane_bytes, it.vbytes);
+      }
     }
     bulk_commit();
-    // The store of chunk k-1 has finished reading its stage once at most one
+    // The stores of item k-1 have finished reading their stage once at most one
     // group (the one just committed) is still pending; that stage is the one
-    // chunk k+stages-1 maps to.
+    // item k+stages-1 maps to.
     bulk_wait_read_1();
     issue_load(k + stages - 1);
   }
@@ -513,7 +599,7 @@ __global__ void __launch_bounds__(256) k_token_major(const __grid_constant__ Tok
     char* pool_p = a.pool.base[shard] + (local * a.page_tokens + tok) * a.token_bytes +
                    (unsigned long long)slab * slab_elems * sizeof(T);
     const longlong2 rq = __ldg(reinterpret_cast<const longlong2*>(a.reqs + r.z));
-    if (!window_ok(r, rq.y, a.status)) continue;
+    if (!window_ok(r, (unsigned long long)rq.x, rq.y, a.status)) continue;
     T* work = reinterpret_cast<T*>(rq.x);
     const unsigned long long T_req = (unsigned long long)rq.y;
     const unsigned long long wtok = r.w + tok;
@@ -631,7 +717,7 @@ __global__ void __launch_bounds__(256) k_token_major16(const __grid_constant__ T
     uint4* pool_p = reinterpret_cast<uint4*>(a.pool.base[shard] + (local * a.page_tokens + tok) * a.token_bytes +
                                              (unsigned long long)slab * slab_words * 4ull);
     const longlong2 rq = __ldg(reinterpret_cast<const longlong2*>(a.reqs + r.z));
-    if (!window_ok(r, rq.y, a.status)) continue;
+    if (!window_ok(r, (unsigned long long)rq.x, rq.y, a.status)) continue;
     unsigned short* work = reinterpret_cast<unsigned short*>(rq.x);
     const unsigned long long T_req = (unsigned long long)rq.y;
     // Element offset of (plane 0, this token, h = 0, first d of the slab); a plane is
@@ -807,7 +893,7 @@ __device__ __forceinline__ TmItem tm16v_item(const TokenMajor16vArgs& a, unsigne
   it.pool_p = reinterpret_cast<uint4*>(a.pool.base[shard] + (local * a.page_tokens + tok) * a.token_bytes) +
               ((unsigned long long)d0 * a.H + h0) * a.LU;
   const longlong2 rq = __ldg(reinterpret_cast<const longlong2*>(a.reqs + r.z));
-  if (!window_ok(r, rq.y, a.status)) return it;
+  if (!window_ok(r, (unsigned long long)rq.x, rq.y, a.status)) return it;
   const unsigned row_elems = a.H * a.D;
   it.work_tok = reinterpret_cast<unsigned short*>(rq.x) + (unsigned long long)(r.w + tok) * row_elems +
                 h0 * a.D + d0;

@@ -263,6 +263,12 @@ class PageMover:
                                      C.c_void_p(self._stream(stream)))
         N.check(rc, "bikv_copy_range")
 
+    def copy_range_engine(self, dst_ptr: int, src_ptr: int, nbytes: int, *, stream=None) -> None:
+        """The same range moved by the copy engines (no kernel, no SM)."""
+        rc = N.lib().bikv_copy_range_engine(C.c_void_p(dst_ptr), C.c_void_p(src_ptr), int(nbytes),
+                                            C.c_void_p(self._stream(stream)))
+        N.check(rc, "bikv_copy_range_engine")
+
     # -- status ------------------------------------------------------------
     def check_status(self) -> None:
         """Synchronising read of the device status words; raises if a kernel's bounded

@@ -111,7 +111,7 @@ const char* bikv_strerror(int status);
 int bikv_last_cuda_error(void);
 /* Number of kernels this library has launched in this process. */
 int64_t bikv_launch_count(void);
-/* Tuning knobs: "ldst_ctas_per_sm", "bulk_ctas_per_sm", "bulk_stages",
+/* Tuning knobs: "ldst_ctas_per_sm", "bulk_ctas_per_sm", "bulk_stages", "bulk_span",
  * "seg_bytes", "auto_variant", "ldst_threads", "tm_threads", "tm16_threads", "tm_max_groups",
  * "tm_tile_kib", "tm_split_tile_kib", "tm_max_heads", "tm_scatter_staged", "tm_gather_stages",
  * "tm_scatter_stages".
@@ -154,6 +154,17 @@ int bikv_plan_validate(const bikv_page_rec* recs, int64_t n_pages,
                        const bikv_pool_desc* pool, const bikv_geometry* geom,
                        int check_overlap);
 
+/*
+ * The rule every kernel applies to a worker-side base address -- a request's KV
+ * tensor (bikv_request_desc.base) or a layer tensor of a paged worker cache --
+ * before it forms an address from it: BIKV_ERR_BAD_ARG for NULL,
+ * BIKV_ERR_ALIGNMENT unless 16-byte aligned, else BIKV_OK.  Host code and device
+ * code share the one function, so a caller that keeps its tables in device memory
+ * can pre-check them with exactly the kernels' rule.  The reference checks nothing
+ * of the kind (SharedMemory/CUDA_Shared/copy_kernel.cu:68-129 launches unchecked).
+ */
+int bikv_check_worker_base(const void* base);
+
 /* ---- gather / scatter (device) ------------------------------------------- */
 /*
  * Gather: for every record, pool page -> request KV window, converting the pool
@@ -165,8 +176,9 @@ int bikv_plan_validate(const bikv_page_rec* recs, int64_t n_pages,
  *   status_dev               device int32[4], zeroed by the caller; word 0
  *                            receives a bikv_status if a bounded device wait
  *                            runs out, or if a record points outside the pool or
- *                            outside its worker tensor: the kernels check every
- *                            record and SKIP a bad one instead of touching memory
+ *                            outside its worker tensor, or selects a request whose
+ *                            base is NULL or not 16-byte aligned: the kernels check
+ *                            every record and SKIP a bad one instead of touching memory
  *                            (records in device memory cannot be checked on the
  *                            host).  May be NULL for BIKV_VARIANT_LDST; bad records
  *                            are then skipped silently.
@@ -253,7 +265,12 @@ int bikv_plan_validate_nhd(const bikv_page_rec* recs, int64_t n_pages, int64_t s
  * BIKV_STATIC_MAX_REQUESTS; larger plans are refused with BIKV_ERR_TOO_LARGE
  * before anything is copied or launched (split the plan, or use bikv_gather_h).
  * The first call on a device looks up the array's device address (with that
- * device current); make that first call outside any stream capture.
+ * device current); make that first call outside any stream capture.  It is also
+ * the moment the CUDA runtime may place the library's device image -- this array
+ * included -- on the GPU (module loading is lazy by default), and that placement
+ * needs free device memory: make one call per device at start-up, BEFORE the
+ * engine reserves HBM, or it can fail with BIKV_ERR_CUDA (out of memory).  A call
+ * with n_pages == 0 does exactly this set-up and launches nothing.
  * Every call on a device shares the one array: it still holds the previous
  * call's plan, nothing in it needs to start at zero (each call overwrites the
  * part it uses), and two calls whose GPU work overlaps -- different streams, or
@@ -288,6 +305,16 @@ int bikv_copy_pages_flat(const void* src, void* dst, const int64_t* src_off_dev,
  * copy is ordered on `stream`.
  */
 int bikv_copy_range(void* dst, const void* src, int64_t bytes, void* stream);
+/*
+ * The same contiguous range moved by the GPU's copy engines instead of a kernel
+ * (one cudaMemcpyAsync with unified addressing; either side may be device memory
+ * of this GPU, a peer or IPC mapping, or pinned host memory).  It occupies no SM,
+ * which suits the large single ranges of post_rdma_write / post_rdma_read
+ * (NetworkTransport/onesided_rdma.h:652-759: one work request per contiguous
+ * range), and it is the independent yardstick the benchmark holds the copy
+ * kernels' NVLink throughput against.  Ordered on `stream`; launches no kernel.
+ */
+int bikv_copy_range_engine(void* dst, const void* src, int64_t bytes, void* stream);
 
 /*
  * Diagnostic with no counterpart in the reference: launches one thread that waits

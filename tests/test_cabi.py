@@ -38,6 +38,16 @@ def test_version_and_strerror(native):
     assert native.bikv_strerror(-99) == b"unknown status"
 
 
+def test_worker_base_rule(native):
+    """The predicate the kernels apply to a worker-side base before forming an address."""
+    f = native.bikv_check_worker_base
+    assert f(None) == N.ERR_BAD_ARG
+    for ok in (16, 4096, 0x7F0000000010, (1 << 47) - 16):
+        assert f(C.c_void_p(ok)) == 0
+    for off in range(1, 16):
+        assert f(C.c_void_p(0x7F0000000000 + off)) == N.ERR_ALIGNMENT, off
+
+
 def test_tuning_knobs(native):
     assert native.bikv_set_tuning(b"nope", 1) == N.ERR_BAD_ARG
     old = native.bikv_get_tuning(b"bulk_stages")

@@ -140,3 +140,36 @@ def test_paged_worker_bad_device_records_are_skipped(cuda):
         assert equal_bits(a, b)
     with pytest.raises(B.BikvError):
         mover.check_status()
+
+
+def test_paged_worker_bad_layer_bases_are_skipped(cuda):
+    """The layer table of a paged worker cache lives in device memory: an entry that is NULL
+    or not 16-byte aligned makes the kernel skip that layer's planes; the other layers are
+    served and the status word names the error."""
+    import ctypes as C
+    g = GEOS["small"]
+    shard_cpu = make_shards(g, 1, 6, 4)[0]
+    shard = shard_cpu.to(cuda)
+    pool = B.ShardedPool.single(shard, g)
+    mover = B.PageMover(cuda)
+    slots = 32
+    gn = g.native()
+    for bad, want in ((8, N.ERR_ALIGNMENT), (None, N.ERR_BAD_ARG)):
+        layers = [torch.zeros(slots + 1, 2, g.n_kv_heads, g.head_dim, dtype=g.dtype, device=cuda)
+                  for _ in range(g.n_layers)]
+        bases = [t.data_ptr() for t in layers]
+        bases[1] = 0 if bad is None else bases[1] + bad
+        table = torch.tensor(bases, dtype=torch.int64, device=cuda)
+        recs = torch.tensor([[2, 16, 0, 0], [4, 5, 0, 16]], dtype=torch.int32, device=cuda)
+        rc = N.lib().bikv_gather_nhd(C.byref(pool.desc), C.byref(gn), C.c_void_p(recs.data_ptr()), recs.shape[0],
+                                     C.c_void_p(table.data_ptr()), slots, C.c_void_p(mover.status.data_ptr()), None)
+        assert rc == 0
+        torch.cuda.synchronize()
+        ref = [torch.zeros(slots + 1, 2, g.n_kv_heads, g.head_dim, dtype=g.dtype) for _ in range(g.n_layers)]
+        O.gather_nhd([shard_cpu], g, [(2, 16, 0, 0), (4, 5, 0, 16)], ref)
+        ref[1].zero_()                                           # the bad layer is left alone
+        for a, b in zip(layers, ref):
+            assert equal_bits(a, b)
+        with pytest.raises(B.BikvError) as e:
+            mover.check_status()
+        assert e.value.status == want

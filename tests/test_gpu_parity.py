@@ -349,6 +349,68 @@ def test_bad_records_in_a_device_plan_are_skipped_not_dereferenced(cuda, layout,
     mover.check_status()
 
 
+# LDST on the paged layout first: its copy loop tolerates any alignment, so this case cannot
+# fault even if the check were missing, and a run that stops at the first failure never
+# reaches the kernels that issue 16-byte and bulk accesses.
+@pytest.mark.parametrize("layout,variant", [(N.POOL_PAGED, "ldst"), (N.POOL_PAGED, "bulk"),
+                                            (N.POOL_TOKEN_MAJOR, "ldst")])
+def test_bad_request_bases_in_a_device_table_are_skipped_not_dereferenced(cuda, layout, variant):
+    """A request table in device memory cannot be checked on the host either.  A record that
+    selects a request whose base is NULL or not 16-byte aligned is skipped before any address
+    is formed from it; records of the other requests are served."""
+    g = KVGeometry(4, 2, 64, 16, torch.float16, layout)
+    shard_cpu = make_shards(g, 1, 8, 2)[0]
+    shard = shard_cpu.to(cuda)
+    pool = B.ShardedPool.single(shard, g)
+    mover = B.PageMover(cuda)
+    out = make_workers(g, [32], cuda)
+    # Backing store for the misaligned request: base + 8 stays inside this allocation.
+    backing = torch.zeros(g.token_elems * 33, dtype=g.dtype, device=cuda)
+    good = [[3, 16, 0, 0], [5, 9, 0, 16]]
+    for bad_base, want in ((backing.data_ptr() + 8, N.ERR_ALIGNMENT), (backing.data_ptr() + 2, N.ERR_ALIGNMENT),
+                           (0, N.ERR_BAD_ARG)):
+        out[0].zero_()
+        reqs = torch.tensor([[out[0].data_ptr(), 32], [bad_base, 32]], dtype=torch.int64, device=cuda)
+        table = torch.tensor(good + [[1, 16, 1, 0], [2, 16, 1, 16]], dtype=torch.int32, device=cuda)
+        mover.gather_dev(pool, table, reqs, variant=VARIANTS[variant])
+        torch.cuda.synchronize()
+        ref = make_workers(g, [32])
+        O.gather([shard_cpu], g, [tuple(r) for r in good], ref)
+        assert equal_bits(out[0], ref[0])
+        assert int(backing.view(torch.int16).ne(0).sum()) == 0
+        with pytest.raises(B.BikvError) as e:
+            mover.check_status()
+        assert e.value.status == want
+        # scatter: the pool stays as it is outside the good pages
+        src = make_workers(g, [32], fill="normal", seed=9)
+        src_gpu = src[0].to(cuda)
+        reqs = torch.tensor([[src_gpu.data_ptr(), 32], [bad_base, 32]], dtype=torch.int64, device=cuda)
+        mover.scatter_dev(pool, table, reqs, variant=VARIANTS[variant])
+        torch.cuda.synchronize()
+        O.scatter([shard_cpu], g, [tuple(r) for r in good], src)
+        assert equal_bits(shard, shard_cpu)
+        with pytest.raises(B.BikvError) as e:
+            mover.check_status()
+        assert e.value.status == want
+
+
+@pytest.mark.parametrize("span", [2, 3, 4, 8])
+def test_bulk_ring_with_several_planes_per_stage(cuda, native, span):
+    """The bulk ring may move `bulk_span` adjacent planes of a page per stage (one load
+    from the pool for all of them on a gather, one store for a full page on a scatter)."""
+    old = native.bikv_get_tuning(b"bulk_span")
+    try:
+        assert native.bikv_set_tuning(b"bulk_span", span) == 0
+        run_case(cuda, SMALL, 3, 11, 7, 6 * 16, N.VARIANT_BULK, seed=span)            # 6 planes: ragged last group
+        run_case(cuda, B.GEO_B, 1, 64, 4, 200, N.VARIANT_BULK, seed=span + 1)
+        run_case(cuda, TINY, 1, 16, 3, 30, N.VARIANT_BULK, seed=span + 2)
+        run_case(cuda, GEOS["C-lite"], 1, 32, 3, 100, N.VARIANT_BULK, seed=span + 3)  # planes in 2 parts: span ignored
+        for tail in (1, 7, 15):
+            run_case(cuda, SMALL, 1, 8, 1, 16 + tail, N.VARIANT_BULK, seed=tail, min_tokens=16 + tail)
+    finally:
+        native.bikv_set_tuning(b"bulk_span", old)
+
+
 def test_one_mover_shared_by_threads_on_their_own_streams(cuda):
     """The reference serves its data methods from a 20-thread gRPC pool
     (distributed_grpc_init.py:127,144).  Eight threads share one PageMover, each on its own

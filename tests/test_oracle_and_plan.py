@@ -202,6 +202,17 @@ def test_owner_split_covers_every_record_exactly_once(native):
         push = split_plans_by_owner(tables, nreq, owner, world, per * 4)
         assert ((push[:, 0] % world) == owner).all()
         seen += len(push)
+        # destinations interleave: no worker's rows are bunched into one stretch of the sweep,
+        # and each worker's rows keep their plan order
+        dest = push[:, 2] // 3
+        for r in range(world):
+            at = np.flatnonzero(dest == r)
+            if len(at) >= 2:
+                assert at[-1] - at[0] >= (len(push) - 1) // 2
+            mine = push[at].copy()
+            mine[:, 2] -= 3 * r
+            rows_r = tables[r][(tables[r][:, 0] % world) == owner]
+            assert np.array_equal(mine, rows_r)
         O.gather(shards, g, [tuple(x) for x in push.tolist()], flat)
     assert seen == sum(len(t) for t in tables)
     for a, b in zip(flat, [t for ts in want for t in ts]):

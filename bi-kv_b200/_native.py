@@ -125,6 +125,8 @@ SIGNATURES = {
     "bikv_copy_pages_flat": (C.c_int, [_P, _P, _P, _P, C.c_int64, C.c_int64, C.c_int32, _P]),
     "bikv_copy_range": (C.c_int, [_P, _P, C.c_int64, _P]),
     "bikv_copy_range_engine": (C.c_int, [_P, _P, C.c_int64, _P]),
+    "bikv_host_register": (C.c_int, [_P, C.c_int64]),
+    "bikv_host_unregister": (C.c_int, [_P]),
     "bikv_selftest_wait_timeout": (C.c_int, [_P, C.c_int64, _P]),
     "bikv_can_access_peer": (C.c_int, [C.c_int, C.c_int, C.POINTER(C.c_int)]),
     "bikv_enable_peer": (C.c_int, [C.c_int, C.c_int]),
@@ -141,6 +143,7 @@ SIGNATURES = {
     "bikv_pm_set_protected": (C.c_int, [_P, C.c_int64]),
     "bikv_pm_remove_protected": (C.c_int, [_P, C.c_int64]),
     "bikv_pm_advance_clock": (C.c_int, [_P, C.c_int64]),
+    "bikv_pm_set_clock": (C.c_int, [_P, C.c_int64]),
     "bikv_pm_free_pages": (C.c_int64, [_P, C.c_int32]),
     "bikv_pm_item_count": (C.c_int64, [_P, C.c_int32]),
     "bikv_pm_evictions": (C.c_int64, [_P]),

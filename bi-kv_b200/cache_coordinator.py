@@ -14,11 +14,20 @@ hit/miss table of the polled requests once their counters have reached ``task_nu
 Differences: the page table is ``PageDirectory`` (tiered policy by default, i.e. the Go page
 manager's priorities; ``policy="lru"`` gives the Python coordinator's); waiting is done on a
 condition variable instead of spinning; TTL demotion runs when ``gc()`` is called (or every
-``gc_interval_s`` seconds on a timer thread) on the monotonic nanosecond clock.
+``gc_interval_s`` seconds on a timer thread).  One time base throughout: the page table's
+clock is moved to the monotonic nanosecond clock before every batch of decisions, so the
+stamp an entry gets when it is loaded or touched and the ``now`` of a later ``gc()`` are both
+nanoseconds, and ``ttl_s`` is an idle time in seconds whenever the first ``gc()`` comes.
+
+A task that cannot be decided (an item larger than a shard, a pool with nothing left to
+evict) and a shard whose RPC fails are logged, answered as CACHE_MISS and counted as
+finished, so pollers are released and the loop thread lives on; the Go coordinator logs and
+returns from the batch in the same situations (``CacheCoordinator.go:239-273``).
 """
 from __future__ import annotations
 
 import json
+import logging
 import threading
 import time
 from collections import deque
@@ -29,6 +38,8 @@ from . import taskinfo as pb
 from .page_directory import PageDirectory
 from .rpc_def import KVCACHE_offset
 from .signals import CACHE_HIT, CACHE_MISS, SIGNAL_CHECK, SIGNAL_RECV, SIGNAL_SEND
+
+log = logging.getLogger("bikv.coordinator")
 
 
 class CacheCoordinator:
@@ -66,6 +77,7 @@ class CacheCoordinator:
                 return G.KVCacheServiceStub(channels[address])
         self._kvcache_stub = kvcache_stub_factory
         self._gc_timer: Optional[threading.Timer] = None
+        self.errors = 0                               # tasks answered as misses after a failure
         self._gc_interval_s = gc_interval_s
 
     # -- helpers ------------------------------------------------------------
@@ -103,6 +115,7 @@ class CacheCoordinator:
         limit = self.kvcache_num * self.page_manager.num_pages
         total = loaded = 0
         with self._lock:
+            self.page_manager.set_clock(time.monotonic_ns())
             for k in ids:
                 tokens = int(data.get(str(k + 2000000 if user_file else k), 0))
                 self.page_manager.load_item(int(k), tokens, 0, "prepared")
@@ -153,6 +166,7 @@ class CacheCoordinator:
     def ReceiveTasksFromScheduler(self, request, context):
         miss: Dict[int, Dict[str, int]] = {}
         with self._lock:
+            self.page_manager.set_clock(time.monotonic_ns())
             for task in request.tasks:
                 entry = miss.setdefault(task.request_id, {"user miss": 0, "item miss": 0})
                 if self.page_manager.access_item(task.id)[0] is None:
@@ -190,10 +204,25 @@ class CacheCoordinator:
             task.cache_pages_list.extend(pages)
         self.finished_counter_table.setdefault(req, 0)
 
+    def _give_up(self, tasks: list, why: str) -> None:
+        """Tasks that were not carried out: their items read as misses, and they count as
+        finished so that nobody waits for them (lock held)."""
+        for task in tasks:
+            self.cache_miss_dict.setdefault(task.request_id, {})[task.id] = CACHE_MISS
+            self.finished_counter_table[task.request_id] = self.finished_counter_table.get(task.request_id, 0) + 1
+        self.errors += len(tasks)
+        log.error("%d task(s) not carried out: %s", len(tasks), why)
+
     def _execute(self, cache_worker: int, tasks: list) -> None:
-        stub = self._kvcache_stub(self._kvcache_address(cache_worker))
-        reply = stub.ReceiveTasksFromCoordinator(pb.TaskInfoList(tasks=tasks))
-        counts = json.loads(reply.msg)
+        try:
+            stub = self._kvcache_stub(self._kvcache_address(cache_worker))
+            reply = stub.ReceiveTasksFromCoordinator(pb.TaskInfoList(tasks=tasks))
+            counts = json.loads(reply.msg)
+        except Exception as e:  # noqa: BLE001  (a shard that is down, a malformed reply)
+            with self._wake:
+                self._give_up(tasks, f"shard {cache_worker}: {type(e).__name__}: {e}")
+                self._wake.notify_all()
+            return
         with self._wake:
             for req, n in counts.items():
                 self.finished_counter_table[int(req)] = self.finished_counter_table.get(int(req), 0) + n
@@ -206,10 +235,18 @@ class CacheCoordinator:
         groups: Dict[int, list] = {}
         with self._wake:
             n = len(self._queue)
+            if n:
+                self.page_manager.set_clock(time.monotonic_ns())
             while self._queue:
                 task = self._queue.popleft()
-                self._decide(task)
+                try:
+                    self._decide(task)
+                except Exception as e:  # noqa: BLE001  (item too large, nothing left to evict)
+                    self._give_up([task], f"item {task.id} of request {task.request_id}: {type(e).__name__}: {e}")
+                    continue
                 groups.setdefault(task.cache_worker, []).append(task)
+            if n:
+                self._wake.notify_all()
         futures = [self._pool.submit(self._execute, cw, tasks) for cw, tasks in groups.items()]
         for f in futures:
             f.result()
@@ -222,7 +259,10 @@ class CacheCoordinator:
                     self._wake.wait(timeout=0.5)
                 if not self._running:
                     return
-            self.process_pending()
+            try:
+                self.process_pending()
+            except Exception:  # noqa: BLE001  (the loop must outlive any one batch)
+                log.exception("batch failed")
 
     def stop(self) -> None:
         with self._wake:

@@ -803,6 +803,18 @@ int bikv_copy_range_engine(void* dst, const void* src, int64_t bytes, void* stre
   return BIKV_OK;
 }
 
+int bikv_host_register(void* ptr, int64_t bytes) {
+  if (!ptr || bytes <= 0) return BIKV_ERR_BAD_ARG;
+  BIKV_CUDA(cudaHostRegister(ptr, (size_t)bytes, cudaHostRegisterPortable | cudaHostRegisterMapped));
+  return BIKV_OK;
+}
+
+int bikv_host_unregister(void* ptr) {
+  if (!ptr) return BIKV_ERR_BAD_ARG;
+  BIKV_CUDA(cudaHostUnregister(ptr));
+  return BIKV_OK;
+}
+
 int bikv_can_access_peer(int device, int peer, int* can) {
   if (!can) return BIKV_ERR_BAD_ARG;
   if (device == peer) {

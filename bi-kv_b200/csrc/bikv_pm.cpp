@@ -243,6 +243,12 @@ int bikv_pm_remove_protected(bikv_pm* pm, int64_t item_id) {
   return BIKV_OK;
 }
 
+int bikv_pm_set_clock(bikv_pm* pm, int64_t now) {
+  if (!pm) return BIKV_ERR_BAD_ARG;
+  if (now > pm->clock) pm->clock = now;
+  return BIKV_OK;
+}
+
 int bikv_pm_advance_clock(bikv_pm* pm, int64_t now) {
   if (!pm) return BIKV_ERR_BAD_ARG;
   if (now > pm->clock) pm->clock = now;

@@ -103,6 +103,10 @@ class PageDirectory:
     def advance_clock(self, now: int) -> None:
         N.check(self._lib.bikv_pm_advance_clock(self._h, now), "bikv_pm_advance_clock")
 
+    def set_clock(self, now: int) -> None:
+        """Moves the clock forward without running the TTL pass (see ``bikv_pm_set_clock``)."""
+        N.check(self._lib.bikv_pm_set_clock(self._h, now), "bikv_pm_set_clock")
+
     def free_pages(self, shard: int) -> int:
         return int(self._lib.bikv_pm_free_pages(self._h, shard))
 

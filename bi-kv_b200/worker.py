@@ -8,12 +8,19 @@ reference's Worker are outside this path and are not built.
 
 The worker owns a packed KV buffer ``compute_buffer`` of shape
 ``[layer, kv, buffer_tokens, head, dim]`` on its GPU.  A combined task's items are
-laid out one after another from token 0 (the reference's running ``dest_offsets``,
-``DistributedStorage/kvcache.py:161-174``).
+laid out one after another (the reference's running ``dest_offsets``,
+``DistributedStorage/kvcache.py:161-174``) inside a token WINDOW of that buffer that
+belongs to the task alone: the coordinator splits a batch by shard and the shards serve
+their groups concurrently, so one worker receives several combined tasks at once, and
+each needs its own place.  (The reference allocates a fresh tensor per call,
+``Worker/Worker.py:162-218``; here windows are handed out from the one buffer, front to
+back, starting over at token 0 when the end is reached -- the ring discipline of the
+reference's staging buffer, ``SharedMemory/CUDA_Shared/ipc_service.cpp:146-168``.)
 """
 from __future__ import annotations
 
-from typing import Dict, Optional, Sequence
+import threading
+from typing import Dict, Optional, Sequence, Tuple
 
 import torch
 
@@ -48,6 +55,11 @@ class Worker:
         self.start_pos = 0
         self.cache_miss_dict: Dict = {}
         self.pool: Optional[ShardedPool] = None
+        # Token windows of compute_buffer, one per combined task (see the module text).
+        self._window_lock = threading.Lock()
+        self._cursor = 0
+        self._reserved: Dict[Tuple[int, int], Tuple[int, int]] = {}
+        self.windows: Dict[Tuple[int, int], Tuple[int, int]] = {}   # (task_type, cache_worker) -> last (start, tokens)
         self.mover = PageMover(self.device)
         # The model-side paged KV cache (``local_kvcache`` of Worker/Worker.py:68-78): one
         # [blocks * block_size, 2, heads, dim] tensor per layer; allocated on demand.
@@ -74,6 +86,52 @@ class Worker:
                 kv.attach_worker(w)
 
     # -- data plane ----------------------------------------------------------
+    @staticmethod
+    def _task_key(task) -> Tuple[int, int]:
+        if isinstance(task, dict):
+            return int(task["task_type"]), int(task["cache_worker"])
+        return int(task.task_type), int(task.cache_worker)
+
+    @staticmethod
+    def _task_tokens(task) -> int:
+        if isinstance(task, dict):
+            return int(sum(p[1] for p in task["id_token_pair"]))
+        return int(sum(p.token_num for p in task.id_token_pair))
+
+    def _bump(self, tokens: int) -> int:
+        if tokens > self.buffer_size:
+            raise N.BikvError(N.ERR_DST_RANGE, "worker buffer too small for the task")
+        if self._cursor + tokens > self.buffer_size:
+            self._cursor = 0
+        start = self._cursor
+        self._cursor += tokens
+        return start
+
+    def reserve_window(self, combined_task_info) -> int:
+        """Reserves the token window the NEXT pull/push of this task's (task_type,
+        cache_worker) will use and returns its first token.  The producer of a RECV's data
+        (the model's prefill) calls this, writes ``compute_buffer[:, :, start:start+tokens]``,
+        and then lets the task run."""
+        tokens = self._task_tokens(combined_task_info)
+        with self._window_lock:
+            start = self._bump(tokens)
+            self._reserved[self._task_key(combined_task_info)] = (start, tokens)
+        return start
+
+    def reset_windows(self) -> None:
+        """Start handing out windows from token 0 again (between batches)."""
+        with self._window_lock:
+            self._cursor = 0
+            self._reserved.clear()
+
+    def _window(self, task, tokens: int) -> int:
+        key = self._task_key(task)
+        with self._window_lock:
+            got = self._reserved.pop(key, None)
+            start = got[0] if got is not None and got[1] == tokens else self._bump(tokens)
+            self.windows[key] = (start, tokens)
+        return start
+
     def _plan(self, task):
         if self.pool is None:
             raise RuntimeError(f"worker rank {self.rank}: no pool attached")
@@ -81,22 +139,28 @@ class Worker:
                                        block_sharded=self.pool.rule == N.SHARD_BLOCK)
         if plan.total_tokens > self.buffer_size:
             raise N.BikvError(N.ERR_DST_RANGE, "worker buffer too small for the task")
-        return plan
+        start = self._window(task, plan.total_tokens)
+        if start:
+            plan.table[:, 3] += start
+            plan.request_tokens[0] += start
+        return plan, start
 
     def pull_pages(self, combined_task_info):
-        """Gather the task's pages into ``compute_buffer[:, :, :tokens]``; returns that view.
+        """Gather the task's pages into its own window ``compute_buffer[:, :, start:start+tokens]``;
+        returns that view (``windows[(task_type, cache_worker)]`` records the window).
         Asynchronous on this GPU's current stream."""
-        plan = self._plan(combined_task_info)
+        plan, start = self._plan(combined_task_info)
         with torch.cuda.device(self.device):
             self.mover.gather(self.pool, plan, self.compute_buffer)
-        return self.compute_buffer[:, :, :plan.total_tokens]
+        return self.compute_buffer[:, :, start:plan.total_tokens]
 
     def push_pages(self, combined_task_info):
-        """Scatter ``compute_buffer[:, :, :tokens]`` into the task's pages."""
-        plan = self._plan(combined_task_info)
+        """Scatter the task's window of ``compute_buffer`` into the task's pages: the window
+        reserved for it with :meth:`reserve_window`, else the next free one."""
+        plan, start = self._plan(combined_task_info)
         with torch.cuda.device(self.device):
             self.mover.scatter(self.pool, plan, self.compute_buffer)
-        return plan.total_tokens
+        return plan.total_tokens - start
 
     def init_local_kvcache(self, max_blocks: int) -> None:
         """Allocates the paged per-layer KV cache with blocks of ``page_size`` tokens (the

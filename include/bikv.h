@@ -325,6 +325,18 @@ int bikv_copy_range_engine(void* dst, const void* src, int64_t bytes, void* stre
  */
 int bikv_selftest_wait_timeout(int32_t* status_dev, int64_t limit_ns, void* stream);
 
+/*
+ * Makes a host range (e.g. a mapping of a POSIX shared-memory block that two
+ * processes share) page-locked and addressable by the GPUs, so that the copy
+ * kernels and bikv_copy_range / bikv_copy_range_engine can read and write it in
+ * place.  This is what stands in for ibv_reg_mr on the 'cpu' buffers of
+ * RDMAOneSidedEndpoint (NetworkTransport/onesided_rdma.h:652-759 copy between
+ * registered buffers; the registration itself is in its allocate_*_memory helpers).
+ * Unregister before unmapping the range.
+ */
+int bikv_host_register(void* ptr, int64_t bytes);
+int bikv_host_unregister(void* ptr);
+
 /* ---- peer mapping -------------------------------------------------------- */
 /* cudaDeviceCanAccessPeer / cudaDeviceEnablePeerAccess for in-process pools;
  * already-enabled is success. */

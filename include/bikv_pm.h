@@ -100,6 +100,12 @@ int bikv_pm_remove_protected(bikv_pm* pm, int64_t item_id);
  * coordinator's periodic ttlGc does (PageManager.go:488-526): demote idle user
  * caches to priority 1, then enforce the priority-1 quota. */
 int bikv_pm_advance_clock(bikv_pm* pm, int64_t now);
+/* Sets the logical clock (never backwards) and nothing else.  A caller whose TTL is in
+ * wall-clock units calls this with its clock before every batch of decisions, so that the
+ * stamps entries receive (clock + 1, + 2, ...) and the `now` of a later
+ * bikv_pm_advance_clock share one time base; the Go coordinator stamps entries with
+ * time.Now() for the same reason (PageManager.go:488-526 compares against LastAccessed). */
+int bikv_pm_set_clock(bikv_pm* pm, int64_t now);
 
 /* Introspection. */
 int64_t bikv_pm_free_pages(const bikv_pm* pm, int32_t shard);

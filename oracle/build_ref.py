@@ -17,7 +17,10 @@ NAME = "bikv_ref_kernel"
 
 
 def main() -> int:
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    # The reference checkout: first argument, else $BIKV_REFERENCE_ROOT, else a directory named
+    # "reference" beside this repository.
+    root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("BIKV_REFERENCE_ROOT") or \
+        os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
     src_dir = os.path.join(root, "Bi-KV", "SharedMemory", "CUDA_Shared")
     kernel = os.path.join(src_dir, "copy_kernel.cu")
     if not os.path.exists(kernel):

@@ -220,7 +220,10 @@ def task_grouping():
 
 
 def main():
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    # The reference checkout: first argument, else $BIKV_REFERENCE_ROOT, else a directory named
+    # "reference" beside this repository.
+    root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("BIKV_REFERENCE_ROOT") or \
+        os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(HERE))), "reference")
     captured = load_reference(root)
     out = {
         "page_manager.json": page_manager_traces(),

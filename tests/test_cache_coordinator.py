@@ -141,3 +141,61 @@ def test_prewarm_from_json(tmp_path):
     cc2, _ = make(n_shards=1)
     assert cc2.read_prepared_data(str(tmp_path / "user_len.json"), str(tmp_path / "user_hot.json")) == 5
     assert len(cc2.page_manager.access_item(3)[1]) == 2
+
+
+class FlakyShard(FakeShard):
+    """Raises on its first call, like a shard that is down, then serves."""
+
+    def __init__(self):
+        super().__init__()
+        self.calls = 0
+
+    def ReceiveTasksFromCoordinator(self, request, context=None):
+        self.calls += 1
+        if self.calls == 1:
+            raise ConnectionError("shard unreachable")
+        return super().ReceiveTasksFromCoordinator(request, context)
+
+
+def test_a_failing_shard_or_an_undecidable_task_does_not_stop_the_loop():
+    import time
+    shard = FlakyShard()
+    cc = CacheCoordinator(1, 5000, [0], [0], 16 * 8, 16, {3: "127.0.0.1"}, None,
+                          kvcache_stub_factory=lambda addr: shard)
+    cc.StartProcessRequest(pb.Empty(), None)
+    try:
+        # batch 1: the shard's RPC raises; batch 2: an item larger than the shard (9 pages > 8)
+        cc.ReceiveTasksFromInferWorker(pb.TaskInfoList(tasks=[task(1, 10, SIGNAL_RECV, task_num=1)]), None)
+        r = cc.PollBatchFromInferWorker(pb.TaskInfoList(tasks=[task(1, 10, SIGNAL_RECV, task_num=1)]), None, timeout_s=10)
+        assert json.loads(r.msg) == {"1": {"10": CACHE_MISS}}
+        cc.ReceiveTasksFromInferWorker(pb.TaskInfoList(tasks=[task(2, 11, SIGNAL_RECV, tokens=16 * 9, task_num=1)]), None)
+        r = cc.PollBatchFromInferWorker(pb.TaskInfoList(tasks=[task(2, 11, SIGNAL_RECV, task_num=1)]), None, timeout_s=10)
+        assert json.loads(r.msg) == {"2": {"11": CACHE_MISS}}
+        assert cc.errors == 2
+        # the loop thread is alive and a later batch is served normally
+        cc.ReceiveTasksFromInferWorker(pb.TaskInfoList(tasks=[task(3, 12, SIGNAL_RECV, task_num=1)]), None)
+        cc.PollBatchFromInferWorker(pb.TaskInfoList(tasks=[task(3, 12, SIGNAL_RECV, task_num=1)]), None, timeout_s=10)
+        assert cc._thread.is_alive()
+        assert [x[:3] for x in shard.seen] == [(3, 12, SIGNAL_RECV)]
+        cc.ReceiveTasksFromInferWorker(pb.TaskInfoList(tasks=[task(4, 12, SIGNAL_CHECK, task_num=1)]), None)
+        r = cc.PollBatchFromInferWorker(pb.TaskInfoList(tasks=[task(4, 12, SIGNAL_CHECK, task_num=1)]), None, timeout_s=10)
+        assert json.loads(r.msg) == {"4": {"12": CACHE_HIT}}
+    finally:
+        cc.stop()
+
+
+def test_ttl_counts_idle_time_from_the_entry_s_own_stamp():
+    """Entries are stamped on the clock gc() compares against: a user cache loaded a moment
+    before the first gc() is not demoted, one idle for longer than the TTL is."""
+    import time
+    cc, shards = make(n_shards=1, ttl_s=5.0)
+    cc.ReceiveTasksFromInferWorker(pb.TaskInfoList(tasks=[task(1, 20, SIGNAL_RECV, task_num=1, kind="user cache",
+                                                               weight=1)]), None)
+    cc.process_pending()
+    assert cc.page_manager.priority(20) == 2
+    cc.gc()                                               # first gc ever, right after the load
+    assert cc.page_manager.priority(20) == 2
+    cc.gc(time.monotonic_ns() + int(4e9))                 # idle for 4 s < ttl
+    assert cc.page_manager.priority(20) == 2
+    cc.gc(time.monotonic_ns() + int(6e9))                 # idle for 6 s > ttl
+    assert cc.page_manager.priority(20) == 1

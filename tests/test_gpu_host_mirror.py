@@ -61,6 +61,7 @@ def test_recv_then_send_through_task_messages(cuda, layout):
             continue
         total = sum(t.token_num for t in tasks[shard])
         data = normal(geom.worker_shape(total), geom.dtype, 50 + shard)
+        worker.reset_windows()
         worker.compute_buffer[:, :, :total] = data.to(cuda)
         conf = kvs[shard].receive_task_info_batch_gprc(tasks[shard])
         assert conf == {7: len(tasks[shard])}
@@ -76,6 +77,7 @@ def test_recv_then_send_through_task_messages(cuda, layout):
     # SEND: same items, looked up through access_item, as a ReceiveTasksFromCoordinator call
     for shard, (data, recs) in sent.items():
         worker.compute_buffer.zero_()
+        worker.reset_windows()
         msgs = []
         for t in tasks[shard]:
             s, pages = mpm.access_item(t.id)
@@ -91,6 +93,83 @@ def test_recv_then_send_through_task_messages(cuda, layout):
     worker.mover.check_status()
 
 
+def test_one_batch_spread_over_two_shards_keeps_every_item_apart(cuda):
+    """A worker whose items sit on two shards receives one combined task per shard, and the
+    coordinator runs the shard groups concurrently: each task has its own window of the
+    worker's buffer, in both directions, so no group overwrites or re-reads another's tokens."""
+    import json
+
+    from bikv_b200.cache_coordinator import CacheCoordinator
+    geom = KVGeometry(2, 2, 64, 16, torch.float16)
+    page, per = 16, 16
+    kvs = [KVCache(3 + 2 * i, per * page, page, 5000, {}, {}, None, geometry=geom, fill=0) for i in range(2)]
+    worker = Worker(2, 5000, 16 * 40, page, 1, {}, {}, None, geometry=geom)
+    Worker.connect(kvs, [worker])
+    addr = {f"127.0.0.1:{5000 + 3 + 2 * i}": kvs[i] for i in range(2)}
+
+    class Local:          # the shard's servicer called in-process
+        def __init__(self, kv):
+            self.kv = kv
+
+        def ReceiveTasksFromCoordinator(self, request, context=None):
+            return self.kv.ReceiveTasksFromCoordinator(request, context)
+
+    cc = CacheCoordinator(1, 5000, [0, 1], [0], per * page, page, {3: "127.0.0.1", 5: "127.0.0.1"}, None, policy="lru",
+                          kvcache_stub_factory=lambda a: Local(addr[a]))
+    items = [(10, 33), (11, 16), (12, 50), (13, 7), (14, 40), (15, 21)]       # ids chosen to hit both shards
+    recv = [pb.TaskInfo(request_id=1, id=i, infer_worker=0, token_num=n, task_type=SIGNAL_RECV, task_num=len(items),
+                        type="item cache") for i, n in items]
+    cc.ReceiveTasksFromInferWorker(pb.TaskInfoList(tasks=recv), None)
+    # Decide first (page placement), so the worker can stage each shard group's tokens in the
+    # window that group will read: what the model's prefill does before the RECV tasks run.
+    with cc._wake:
+        decided = list(cc._queue)
+        cc._queue.clear()
+        for t in decided:
+            cc._decide(t)
+    groups = {}
+    for t in decided:
+        groups.setdefault(t.cache_worker, []).append(t)
+    assert len(groups) == 2, "the case must spread over both shards"
+    data = {}
+    worker.reset_windows()
+    for cw, ts in groups.items():
+        n = sum(t.token_num for t in ts)
+        combined = {"task_type": SIGNAL_RECV, "cache_worker": cw, "id_token_pair": [(t.id, t.token_num) for t in ts]}
+        start = worker.reserve_window(combined)
+        data[cw] = normal(geom.worker_shape(n), geom.dtype, 70 + cw)
+        worker.compute_buffer[:, :, start:start + n] = data[cw].to(cuda)
+    from concurrent.futures import ThreadPoolExecutor
+    with ThreadPoolExecutor(2) as ex:       # the groups run side by side, as process_pending runs them
+        list(ex.map(lambda kv_ts: cc._execute(*kv_ts), groups.items()))
+    torch.cuda.synchronize()
+    shards_ref = [torch.zeros(geom.pool_shape(per), dtype=geom.dtype) for _ in range(2)]
+    for cw, ts in groups.items():
+        recs = O.plan_records([list(t.cache_pages_list) for t in ts], [t.token_num for t in ts], page,
+                              item_shard=[cw] * len(ts), pages_per_shard=per)
+        O.scatter(shards_ref, geom, recs, [data[cw]], N.SHARD_BLOCK)
+    for i in (0, 1):
+        assert equal_bits(kvs[i].cuda_cache_data, shards_ref[i])
+    # SEND through the whole coordinator path: CHECK -> hit -> one group per shard, concurrently
+    worker.compute_buffer.zero_()
+    worker.reset_windows()
+    check = [pb.TaskInfo(request_id=2, id=i, infer_worker=0, token_num=n, task_type=4, task_num=len(items),
+                         type="item cache") for i, n in items]
+    cc.ReceiveTasksFromInferWorker(pb.TaskInfoList(tasks=check), None)
+    assert cc.process_pending() == len(items)
+    reply = cc.PollBatchFromInferWorker(pb.TaskInfoList(tasks=check), None, timeout_s=10)
+    assert set(json.loads(reply.msg)["2"].values()) == {1}
+    torch.cuda.synchronize()
+    seen = set()
+    for cw in groups:
+        start, n = worker.windows[(SIGNAL_SEND, cw)]
+        assert n == data[cw].shape[2]
+        assert equal_bits(worker.compute_buffer[:, :, start:start + n], data[cw])
+        seen |= set(range(start, start + n))
+    assert len(seen) == sum(n for _, n in items), "windows must not overlap"
+    worker.mover.check_status()
+
+
 def test_worker_servicer_methods_take_combined_messages(cuda):
     geom = KVGeometry(2, 2, 64, 16, torch.bfloat16)
     kv = KVCache(3, 16 * 8, 16, 5000, {}, {}, None, geometry=geom, fill=0)
@@ -102,6 +181,7 @@ def test_worker_servicer_methods_take_combined_messages(cuda):
     w.compute_buffer[:, :, :37] = data.to(cuda)
     w.SendKVCacheData(msg, None)
     w.compute_buffer.zero_()
+    w.reset_windows()
     w.RecvKVCacheData(msg, None)
     torch.cuda.synchronize()
     assert equal_bits(w.compute_buffer[:, :, :37], data)

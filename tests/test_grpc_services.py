@@ -97,6 +97,7 @@ def test_transfers_driven_through_grpc(cuda):
             assert json.loads(stub.ReceiveTasksFromCoordinator(pb.TaskInfoList(tasks=recv), timeout=30).msg) == {"5": 2}
             torch.cuda.synchronize()
             worker.compute_buffer.zero_()
+            worker.reset_windows()
             send = [pb.TaskInfo(request_id=6, id=t.id, infer_worker=0, cache_worker=0, token_num=t.token_num,
                                 task_type=SIGNAL_SEND, cache_pages_list=list(t.cache_pages_list)) for t in recv]
             assert json.loads(stub.ReceiveTasksFromCoordinator(pb.TaskInfoList(tasks=send), timeout=30).msg) == {"6": 2}
@@ -180,6 +181,7 @@ def test_full_chain_coordinator_shards_worker_over_grpc(cuda):
             stub.PollBatchFromInferWorker(recv, timeout=60)
             torch.cuda.synchronize()
             worker.compute_buffer.zero_()
+            worker.reset_windows()
             check = pb.TaskInfoList(tasks=[pb.TaskInfo(request_id=2, id=42, infer_worker=0, token_num=50,
                                                        task_type=4, task_num=1, type="item cache")])
             stub.ReceiveTasksFromInferWorker(check, timeout=10)

@@ -8,7 +8,8 @@ entry point uses it.  The test drives the entry point through the C ABI (ctypes,
 pointers) twice in a row -- the second plan is shorter, so the staging area still
 holds the tail of the first -- and requires the worker tensors to equal, bit for bit,
 what the ordinary entry point (bikv_gather_h with a caller-provided staging buffer)
-produces for the same plans.  This file sorts last so that a run which stops at the
+produces for the same plans, and what the CPU oracle computes from the same pool and plan,
+so the check does not hang on the entry point it mirrors.  This file sorts last so that a run which stops at the
 first failure has already run every other test; it does not depend on them.
 """
 import ctypes as C
@@ -19,6 +20,7 @@ import torch
 
 from bikv_b200 import _native as N
 from bikv_b200.geometry import KVGeometry
+from oracle import bikv_oracle as O
 
 pytestmark = pytest.mark.gpu
 
@@ -58,7 +60,8 @@ def test_static_gather_matches_ordinary_gather_twice(native, cuda):
     geom = KVGeometry(4, 2, 64, 16, torch.bfloat16)
     n_pages = 256
     gen = torch.Generator().manual_seed(42)
-    shard = torch.randn(geom.pool_shape(n_pages), generator=gen).to(geom.dtype).to(cuda)
+    shard_cpu = torch.randn(geom.pool_shape(n_pages), generator=gen).to(geom.dtype)
+    shard = shard_cpu.to(cuda)
     pool = N.PoolDesc()
     pool.shard_base[0] = shard.data_ptr()
     pool.n_shards, pool.shard_rule, pool.pages_per_shard = 1, N.SHARD_MOD, n_pages
@@ -71,10 +74,27 @@ def test_static_gather_matches_ordinary_gather_twice(native, cuda):
         got = [torch.zeros_like(t) for t in want]
         assert _gather(native, "ordinary", pool, geom, table, want, cuda, scratch) == 0
         assert _gather(native, "static", pool, geom, table, got, cuda) == 0
-        for a, b in zip(got, want):
+        oracle = [torch.zeros(geom.worker_shape(int(t)), dtype=geom.dtype) for t in tokens]
+        O.gather([shard_cpu], geom, [tuple(r) for r in table.tolist()], oracle)
+        for a, b, c in zip(got, want, oracle):
             assert torch.equal(a.view(torch.int16), b.view(torch.int16)), f"call {call}"
+            assert torch.equal(a.cpu().view(torch.int16), c.view(torch.int16)), f"call {call} against the oracle"
         assert any(int(t.view(torch.int16).ne(0).sum()) > 0 for t in got)
     assert native.bikv_launch_count() - launches == 4
+
+
+def test_static_gather_with_an_empty_plan_is_the_start_up_call(native, cuda):
+    """n_pages == 0 launches nothing but still resolves the staging array's address on the
+    device: the call an engine makes at start-up, before it reserves HBM."""
+    geom = KVGeometry(2, 2, 64, 16, torch.float16)
+    shard = torch.zeros(geom.pool_shape(4), dtype=geom.dtype, device=cuda)
+    pool = N.PoolDesc()
+    pool.shard_base[0] = shard.data_ptr()
+    pool.n_shards, pool.shard_rule, pool.pages_per_shard = 1, N.SHARD_MOD, 4
+    g = geom.native()
+    launches = native.bikv_launch_count()
+    assert native.bikv_gather_h_static(C.byref(pool), C.byref(g), None, 0, None, 0, 1, N.VARIANT_LDST, None, None) == 0
+    assert native.bikv_launch_count() == launches
 
 
 def test_static_gather_refuses_oversized_plans(native, cuda):

@@ -18,6 +18,10 @@ Differences that a caller can observe:
     ``TimeoutError``, where the reference blocks for ever;
   * the control block also records the element type, and bf16 / fp32 transfers are accepted
     (the reference hard-codes fp16 on the receiving side, ``ipc_service.cpp:155-158``);
+  * the block keeps the description (offset, size, shape, type) of each of the last 64
+    transfers, not only of the latest, so the k-th ``consumer_receive`` returns the k-th
+    transfer even when the producer has run ahead (its DATA is still overwritten once the
+    ring wraps onto it, as in the reference);
   * copies run on torch's current stream, which ``producer_*`` synchronises before posting
     (the reference calls ``cudaDeviceSynchronize``);
   * a producer in the consumer's own process attaches to the buffer directly (CUDA does not
@@ -58,7 +62,13 @@ _FIELDS = struct.Struct("<QiiqQQQQQQ5q64sq")
 # magic, device_id, dtype_code, consumer_pid, buffer_size, current_offset, last_valid_offset,
 # data_size, tensor_dim, transfers, tensor_shape[5], cuda_handle[64], handle_offset
 _HOST_AT = 2 * _SEM_BYTES + _FIELDS.size
-_BLOCK_BYTES = _HOST_AT + 256
+# One descriptor per transfer in a ring of _DESCS entries: the reference keeps only the LAST
+# transfer's shape and offset in the block, so a consumer that lags behind a producer reads a
+# later transfer's description; here the k-th receive reads the k-th transfer's own.
+_DESC = struct.Struct("<QQQQi5q")          # transfer number (from 1), offset, size, dim, dtype, shape[5]
+_DESCS = 64
+_DESC_AT = _HOST_AT + 256
+_BLOCK_BYTES = _DESC_AT + _DESCS * _DESC.size
 _MAGIC = 0x42494B5649504331           # "BIKVIPC1"
 _DTYPES = [torch.float16, torch.bfloat16, torch.float32, torch.float64, torch.uint8, torch.int32]
 _libc = C.CDLL(None, use_errno=True)
@@ -116,6 +126,13 @@ class _Control:
     def write(self, fields: list) -> None:
         _FIELDS.pack_into(self.map, 2 * _SEM_BYTES, *fields)
 
+    def read_desc(self, transfer: int) -> tuple:
+        return _DESC.unpack_from(self.map, _DESC_AT + (transfer % _DESCS) * _DESC.size)
+
+    def write_desc(self, transfer: int, at: int, size: int, shape, dtype_code: int) -> None:
+        _DESC.pack_into(self.map, _DESC_AT + (transfer % _DESCS) * _DESC.size, transfer, at, size, len(shape),
+                        dtype_code, *(list(shape) + [0] * (5 - len(shape))))
+
     def close(self) -> None:
         self._anchor = None
         try:
@@ -129,6 +146,7 @@ class _Consumer:
         self.device = torch.device(f"cuda:{device_id}")
         self.ctrl = _Control(_shm_path(shm_name), create=True)
         self.buffer = torch.empty(buffer_size, dtype=torch.uint8, device=self.device)
+        self.taken = 0                                   # transfers this consumer has received
         handle = C.create_string_buffer(64)
         off = C.c_int64(0)
         N.check(N.lib().bikv_pool_export(C.c_void_p(self.buffer.data_ptr()), handle, C.byref(off)), "bikv_pool_export")
@@ -149,9 +167,13 @@ class _Consumer:
             if err == 110:        # ETIMEDOUT
                 raise TimeoutError(f"consumer_receive: nothing was sent within {timeout_s} s")
             raise RuntimeError(f"consumer_receive sem_wait failed: errno {err}")
-        f = self.ctrl.read()
-        dtype, last, size, dim, shape = _DTYPES[f[2]], f[6], f[7], f[8], f[10:15]
-        return self.buffer[last:last + size].view(dtype).view(tuple(shape[:dim]))
+        self.taken += 1
+        d = self.ctrl.read_desc(self.taken)
+        if d[0] != self.taken:
+            raise RuntimeError(f"consumer_receive: transfer {self.taken} was overrun (the producer is more than "
+                               f"{_DESCS} transfers ahead)")
+        at, size, dim, dtype, shape = d[1], d[2], d[3], _DTYPES[d[4]], d[5:10]
+        return self.buffer[at:at + size].view(dtype).view(tuple(shape[:dim]))
 
     def cleanup(self) -> None:
         _libc.sem_destroy(self.ctrl.sem_start)
@@ -201,6 +223,7 @@ class _Producer:
         f[8] = len(shape)
         f[9] += 1
         f[10:15] = list(shape) + [0] * (5 - len(shape))
+        self.ctrl.write_desc(f[9], at, nbytes, shape, f[2])
         self.ctrl.write(f)
         _libc.sem_post(self.ctrl.sem_start)
 

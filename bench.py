@@ -65,10 +65,10 @@ def parse_args():
                     help="side measurement: time one direction only (all ranks then move data the same way)")
     ap.add_argument("--worker-layout", default="contiguous", choices=["contiguous", "nhd"],
                     help="nhd = the worker's paged KV, one [slot, kv, head, dim] tensor per layer (side measurement)")
-    ap.add_argument("--gather-mode", default="pull", choices=["pull", "push"],
-                    help="N > 1: pull = the worker's GPU reads remote pages (loads over NVLink; the default, and the "
-                         "faster one: 7.55 against 8.28 ms per gather on 2 GPUs); push = the GPU that owns a page "
-                         "writes it into the worker's tensor, as the reference's shard does on SEND (side measurement)")
+    ap.add_argument("--gather-mode", default="push", choices=["pull", "push"],
+                    help="N > 1: push = the GPU that owns a page writes it into the worker's tensor, as the reference's "
+                         "shard does on SEND (stores over NVLink need no request packets: 6.99 ms per gather on 2 GPUs); "
+                         "pull = the worker's GPU reads remote pages (loads over NVLink: 7.70 ms)")
     ap.add_argument("--small", action="store_true", help="profiling-sized case (2,048-page pool, 8 requests)")
     ap.add_argument("--tune", action="append", default=[], metavar="KNOB=VALUE")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -254,8 +254,8 @@ def config_dict(args, w):
         c["workload"] += " [SMALL profiling case]"
     if args.only != "both":
         c["workload"] += f" [SIDE MEASUREMENT: {args.only} only]"
-    if args.gather_mode != "pull" and args.gpus > 1:
-        c["workload"] += " [SIDE MEASUREMENT: gather pushed by the pages' owner]"
+    if args.gather_mode != "push" and args.gpus > 1:
+        c["workload"] += " [SIDE MEASUREMENT: gather pulled by the worker's GPU]"
     if args.worker_layout != "contiguous":
         c["workload"] += " [SIDE MEASUREMENT: worker KV paged, one [slot, kv, head, dim] tensor per layer]"
     if args.pages_from != "all":
@@ -414,113 +414,268 @@ def run_config4(ctx):
     """Configuration 4: N/2 KVCache-shard GPUs + N/2 worker GPUs, config-1 geometry.  100,000 users
     ~ Zipf(1.1), cached prefixes lognormal(median 1024, sigma 0.8) in [128, 8192] (sigma is not given
     by the configuration; 0.8 as in configuration 1), new tokens U[32,256] written back, LRU eviction by
-    the MultiPageManager, batches of 64.  Every page a worker touches is remote.  Reports pages/s
-    (wall clock, host planning included, and device time only) and the hit rate."""
+    the page directory, batches of 64.  Every page a worker touches is remote.
+
+    Who moves what.  Stores are the better NVLink operation for a kernel, and one GPU that loads and
+    stores remotely at the same time gets little more than either alone (two B200s, one GPU driving:
+    783 GB/s pulling, 715 pushing, 760-910 doing both; the copy engines reach 1,554 there).  So each
+    direction is driven by the GPU that holds the source, with stores only: the SHARD GPUs push the
+    hit prefixes of batch k+1 into the workers' tensors (the shard is the active side of a SEND in
+    the reference too, ``DistributedStorage/kvcache.py:96-113``) while the WORKER GPUs push batch k's
+    missed prefixes and new tokens into the pool.  The two run at the same time -- they load
+    opposite directions of every link -- and one host barrier over all ranks ends the pair.
+
+    Hazard: a prefix stored by batch k and read by batch k+1.  The planner sees it (page ids of
+    the two plans intersect); those gather rows wait, on every shard, for a barrier behind the
+    workers' scatters, the rest overlaps them.  Planning (all workers' shares, replicated on every
+    rank so that all hold the same page directory) runs on a host thread ahead of the kernels.
+
+    Before the timed run a shorter stream goes through the same pipeline with closed-form
+    contents: every prefix a miss stores is a function of (user, token, word), and every prefix
+    a later hit receives -- from whichever shard, for whichever worker -- is compared against it
+    on the device.  Reports pages/s (wall clock, and device time only) and the hit rate."""
+    import ctypes as C
+    import queue
+    import threading
+
+    import numpy as np
     import torch
     import torch.distributed as dist
 
     import bikv_b200 as B
     from bikv_b200 import _native as N
+    from bikv_b200 import selfcheck as S
     from bikv_b200 import workloads as W
     from bikv_b200.coordinator import NativePrefixCacheCoordinator, PrefixCacheCoordinator, PrefixReuseWorkload
+    from bikv_b200.plan import Plan
+    from bikv_b200.push import split_plans_by_owner
 
-    args, rank, world, dev, lib, multi = (ctx[k] for k in ("args", "rank", "world", "dev", "lib", "multi"))
+    args, rank, world, dev, lib = (ctx[k] for k in ("args", "rank", "world", "dev", "lib"))
     if world < 2 or world % 2:
         raise SystemExit("config4 needs an even number of GPUs >= 2 (half shards, half workers)")
     n_shards = n_workers = world // 2
     is_shard = rank < n_shards
+    me = rank if is_shard else rank - n_shards
     geom = W.GEO_B
-    worker_ranks = list(range(n_shards, world))
-    wgroup = dist.new_group(ranks=worker_ranks, backend="gloo")
+    group = ctx["cpu_group"]
+    per_worker = (64 + n_workers - 1) // n_workers
+    arena_elems = geom.token_elems * (8192 + 256) * per_worker
+
     def note(msg):
         print(f"[config4 rank {rank}] {msg}", file=sys.stderr, flush=True)
 
-    handles = [None] * world
-    shard = None
+    # ---- memory: a shard per shard rank, two arenas per worker rank, everything mapped everywhere needed ----
+    shard = arenas = None
     if is_shard:
         shard = torch.zeros(geom.pool_shape(args.pool_pages), dtype=geom.dtype, device=dev)
-        mine = B.ShardedPool.export_handle(shard)
+        mine = [B.ShardedPool.export_handle(shard)]
     else:
-        mine = None
-    dist.all_gather_object(handles, mine, group=ctx["cpu_group"])
-    note("handles exchanged")
-    result = None
-    if not is_shard:
-        import ctypes as C
-        bases, imported = [], []
-        for h in handles[:n_shards]:
-            out = C.c_void_p()
-            N.check(lib.bikv_pool_import(h[0], int(h[1]), C.byref(out)), "bikv_pool_import")
-            bases.append(int(out.value))
-            imported.append((int(out.value), int(h[1])))
-        pool = B.ShardedPool(bases, args.pool_pages, geom, rule=N.SHARD_BLOCK, device=dev, imported=imported)
-        me = rank - n_shards
-        wl = PrefixReuseWorkload(seed=0, n_workers=n_workers, n_requests=args.c4_requests, batch=64)
-        co = (NativePrefixCacheCoordinator(n_shards, args.pool_pages, geom.page_tokens) if args.c4_planner == "native"
-              else PrefixCacheCoordinator(n_shards, args.pool_pages, geom.page_tokens, order="fast"))
-        per_worker = (64 + n_workers - 1) // n_workers
-        arena = torch.zeros(geom.token_elems * (8192 + 256) * per_worker, dtype=geom.dtype, device=dev)
-        mover = B.PageMover(dev, variant=ctx["variant"])
-        stream = torch.cuda.current_stream(dev)
-        ev = []
-        pages = payload = 0
+        # batch k+1 is gathered into one arena while batch k is scattered out of the other
+        arenas = [torch.zeros(arena_elems, dtype=geom.dtype, device=dev) for _ in range(2)]
+        mine = [B.ShardedPool.export_handle(a) for a in arenas]
+    handles = [None] * world
+    dist.all_gather_object(handles, mine, group=group)
+    mapped = []
+
+    def open_handle(h):
+        out = C.c_void_p()
+        N.check(lib.bikv_pool_import(h[0], int(h[1]), C.byref(out)), "bikv_pool_import")
+        mapped.append((int(out.value), int(h[1])))
+        return int(out.value)
+
+    if is_shard:
+        # the pool as this shard addresses it: only its own pages are ever named in its plans
+        pool = B.ShardedPool([shard.data_ptr()] * n_shards, args.pool_pages, geom, rule=N.SHARD_BLOCK, device=dev,
+                             keepalive=[shard])
+        arena_base = [[open_handle(h) for h in handles[n_shards + w]] for w in range(n_workers)]
+    else:
+        pool = B.ShardedPool([open_handle(handles[s][0]) for s in range(n_shards)], args.pool_pages, geom,
+                             rule=N.SHARD_BLOCK, device=dev)
+    mover = B.PageMover(dev, variant=ctx["variant"])
+    stream = torch.cuda.Stream(dev)
+    tables = [torch.empty((per_worker * (n_workers if is_shard else 1), 2), dtype=torch.int64).pin_memory()
+              for _ in range(8)]
+    rw = geom.row_elems * geom.elt_bytes // 4
+    ok_dev = torch.ones((), dtype=torch.bool, device=dev)
+
+    def make_coordinator():
+        return (NativePrefixCacheCoordinator(n_shards, args.pool_pages, geom.page_tokens)
+                if args.c4_planner == "native"
+                else PrefixCacheCoordinator(n_shards, args.pool_pages, geom.page_tokens, order="fast"))
+
+    def planner(wl, co, out_q):
+        """Every worker's share of every batch, and which gather rows read a page the batch before
+        writes (decided over ALL workers, so every rank decides alike)."""
+        prev_written = np.zeros(0, dtype=np.int32)
+        try:
+            for batch in wl.batches():
+                plans = [co.plan_batch([r for r in batch if r.worker == k]) for k in range(n_workers)]
+                late_masks = [np.isin(p.gather.table[:, 0], prev_written) for p in plans]
+                prev_written = np.concatenate([p.scatter.table[:, 0] for p in plans])
+                out_q.put((plans, late_masks, any(bool(m.any()) for m in late_masks)))
+        finally:
+            out_q.put(None)
+
+    def words(arena, off_elems, tokens):
+        n = geom.token_elems * tokens
+        return arena[off_elems:off_elems + n].view(torch.int32).view(geom.planes, tokens, rw)
+
+    def prefix_words(user, tokens):
+        """Closed form of a user's cached prefix: word (plane, token, w) = mix(user, ...)."""
+        return S.worker_words(geom, 0, int(user) & 0xFFFFF, tokens, 0, tokens, dev)
+
+    def shard_rows(plans, masks, k, late):
+        """This shard's rows of all workers' gather plans for batch k (the early or the late
+        ones), destinations interleaved, and the request table of the workers' arenas."""
+        tabs = [p.gather.table[m if late else ~m] for p, m in zip(plans, masks)]
+        nreq = [len(p.requests) for p in plans]
+        rows = split_plans_by_owner(tabs, nreq, me, n_shards, args.pool_pages, rule=N.SHARD_BLOCK)
+        return Plan.from_table(rows, sum(nreq), transient=True)
+
+    def run_stream(wl, co, check):
+        q = queue.Queue(maxsize=3)
+        th = threading.Thread(target=planner, args=(wl, co, q), daemon=True)
+        th.start()
+        pages = payload = n_steps = n_late = 0
+        spans = []
         launches0 = lib.bikv_launch_count()
-        dist.barrier(group=wgroup)
         torch.cuda.synchronize()
-        note("pool mapped, arena ready, starting batches")
+        dist.barrier(group=group)
         t0 = time.perf_counter()
-        for batch in wl.batches():
-            plans = [co.plan_batch([r for r in batch if r.worker == k]) for k in range(n_workers)]
-            bp = plans[me]
-            tensors = _carve(arena, geom, bp.tokens)
-            e = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
-            e[0].record(stream)
-            mover.gather(pool, bp.gather, tensors)
-            e[1].record(stream)
+        prev = None          # worker: (share, arena index, table, offsets) whose scatter is due
+        k = 0
+        drained = False
+        while True:
+            item = None if drained else q.get()
+            drained = item is None
+            if drained and prev is None:
+                break
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            has_late = False
+            cur = None
+            if item is not None:
+                plans, masks, has_late = item
+                table = tables[k % len(tables)]
+                if is_shard:
+                    tn, at = table.numpy(), 0
+                    for w, p in enumerate(plans):
+                        offs = np.asarray(_arena_offsets(geom, p.tokens), dtype=np.int64)
+                        tn[at:at + len(offs), 0] = arena_base[w][k % 2] + offs * geom.elt_bytes
+                        tn[at:at + len(offs), 1] = p.tokens
+                        at += len(offs)
+                    table = table[:at]
+                    cur = True
+                else:
+                    bp = plans[me]
+                    offs = _arena_offsets(geom, bp.tokens)
+                    table = table[:len(bp.tokens)]
+                    tn = table.numpy()
+                    tn[:, 0] = arenas[k % 2].data_ptr() + np.asarray(offs, dtype=np.int64) * geom.elt_bytes
+                    tn[:, 1] = bp.tokens
+                    cur = (bp, k % 2, table, offs)
+                    g = bp.gather.table
+                    pages += len(g) + bp.scatter.n_pages
+                    payload += (int(g[:, 1].sum()) + int(bp.scatter.table[:, 1].sum())) * geom.bytes_per_token
+            # -- the stores of this step --
+            if is_shard:
+                if item is not None:
+                    mover.gather_table(pool, shard_rows(plans, masks, k, late=False), table, stream=stream)
+            elif prev is not None:
+                pbp, pa, ptable, poffs = prev
+                if check:
+                    # what the model would have computed: the prefixes this batch stores
+                    stored = set(int(r) for r in pbp.scatter.table[pbp.scatter.table[:, 3] == 0, 2])
+                    with torch.cuda.stream(stream):
+                        for i, r in enumerate(pbp.requests):
+                            if i in stored and not pbp.hit[i]:
+                                words(arenas[pa], poffs[i], r.tokens)[:, :r.prefix_tokens] = \
+                                    prefix_words(r.user, r.prefix_tokens)
+                mover.scatter_table(pool, pbp.scatter, ptable, stream=stream)
+            if has_late:
+                # rows that read what the workers are writing right now: once every worker's
+                # scatter has landed
+                if not is_shard:
+                    stream.synchronize()
+                dist.barrier(group=group)
+                if is_shard:
+                    mover.gather_table(pool, shard_rows(plans, masks, k, late=True), table, stream=stream)
+                n_late += 1
+            e1.record(stream)
             stream.synchronize()
-            dist.barrier(group=wgroup)
-            e[2].record(stream)
-            mover.scatter(pool, bp.scatter, tensors)
-            e[3].record(stream)
-            stream.synchronize()
-            dist.barrier(group=wgroup)
-            ev.append(e)
-            pages += bp.gather.n_pages + bp.scatter.n_pages
-            payload += (int(bp.gather.table[:, 1].sum()) + int(bp.scatter.table[:, 1].sum())) * geom.bytes_per_token
+            dist.barrier(group=group)
+            spans.append((e0, e1))
+            n_steps += 1
+            if check and not is_shard and cur is not None:
+                # This step's gather is complete: every shard has passed the barrier above.  The
+                # comparison runs on this stream, which the next step synchronises before its own
+                # barrier, i.e. before any shard writes this arena again.
+                cbp, ca, _, coffs = cur
+                with torch.cuda.stream(stream):
+                    for i, r in enumerate(cbp.requests):
+                        if cbp.hit[i]:
+                            got = words(arenas[ca], coffs[i], r.tokens)[:, :r.prefix_tokens]
+                            ok_dev.logical_and_((got == prefix_words(r.user, r.prefix_tokens)).all())
+            prev = cur if not is_shard else (True if item is not None else None)
+            if is_shard and drained:
+                prev = None
+            k += 1
         torch.cuda.synchronize()
         wall = time.perf_counter() - t0
-        note(f"{len(ev)} batches done in {wall:.2f} s")
+        th.join()
         mover.check_status()
-        dev_ms = sum(e[0].elapsed_time(e[1]) + e[2].elapsed_time(e[3]) for e in ev)
-        t = torch.tensor([wall, dev_ms], dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=wgroup)
-        tot = torch.tensor([float(pages), float(payload), float(lib.bikv_launch_count() - launches0)], dtype=torch.float64)
-        dist.all_reduce(tot, op=dist.ReduceOp.SUM, group=wgroup)
-        if me == 0:
-            wall, dev_ms = t.tolist()
-            result = {
-                "metric": "kv_pages_per_second", "value": tot[0].item() / wall, "unit": "pages/s", "n_gpus": world,
-                "steps": len(ev), "warmup": 0, "ms_per_step": wall / len(ev) * 1e3, "higher_is_better": True,
-                "scaling": "weak", "vs_baseline": None, "dtype": "u16", "data": "synthetic",
-                "config": {"workload": f"config4: {n_shards} shard GPUs + {n_workers} worker GPUs, config-1 geometry, "
-                                       f"{wl.n_users} users Zipf(1.1), {wl.n_requests} requests in batches of 64, LRU "
-                                       f"eviction [ADDITIONAL MEASUREMENT]", "pool_pages_per_shard": args.pool_pages},
-                "hit_rate": co.hit_rate, "GBps_wall": tot[1].item() / wall / 1e9,
-                "pages_per_s_device_only": tot[0].item() / (dev_ms / 1e3),
-                "GBps_device_only": tot[1].item() / (dev_ms / 1e3) / 1e9,
-                "nvlink_GBps_per_worker_device_only": tot[1].item() / n_workers / (dev_ms / 1e3) / 1e9,
-                "host_planning": ("native page directory (bikv_pm_plan_prefix_batch)" if args.c4_planner == "native"
-                                  else "Python page managers with order='fast'") + ", replicated on every worker",
-                "gpu_launches": int(tot[2].item()),
-            }
-        pool.close()
-    # shard ranks wait here while the workers run
-    note("waiting for results")
-    out = [None] * world
-    dist.all_gather_object(out, result, group=ctx["cpu_group"])
+        dev_ms = sum(a.elapsed_time(b) for a, b in spans)
+        return dict(wall=wall, dev_ms=dev_ms, pages=pages, payload=payload, steps=n_steps, late=n_late,
+                    launches=lib.bikv_launch_count() - launches0, hit_rate=co.hit_rate)
+
+    # ---- closed-form pass over a shorter stream (same pipeline, contents checked) ----
+    verified = None
+    if not args.no_verify:
+        wl = PrefixReuseWorkload(seed=1, n_workers=n_workers, n_requests=min(args.c4_requests, 1920), batch=64)
+        run_stream(wl, make_coordinator(), check=True)
+        t_ok = torch.tensor([float(bool(ok_dev.item()))], dtype=torch.float64)
+        dist.all_reduce(t_ok, op=dist.ReduceOp.MIN, group=group)
+        verified = bool(t_ok[0])
+        if not verified:
+            raise SystemExit("bench.py config4: a gathered prefix differs from what was stored")
+    # ---- the timed run ----
+    wl = PrefixReuseWorkload(seed=0, n_workers=n_workers, n_requests=args.c4_requests, batch=64)
+    co = make_coordinator()
+    r = run_stream(wl, co, check=False)
+    note(f"{r['steps']} pipeline steps in {r['wall']:.2f} s")
+    t = torch.tensor([r["wall"], r["dev_ms"]], dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
+    tot = torch.tensor([float(r["pages"]), float(r["payload"]), float(r["launches"])], dtype=torch.float64)
+    dist.all_reduce(tot, op=dist.ReduceOp.SUM, group=group)
     if rank == 0:
-        print(json.dumps(next(r for r in out if r is not None)), flush=True)
-    del shard
+        wall, dev_ms = t.tolist()
+        line = {
+            "metric": "kv_pages_per_second", "value": tot[0].item() / wall, "unit": "pages/s", "n_gpus": world,
+            "steps": r["steps"], "warmup": 0, "ms_per_step": wall / r["steps"] * 1e3, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "u16", "data": "synthetic",
+            "config": {"workload": f"config4: {n_shards} shard GPUs + {n_workers} worker GPUs, config-1 geometry, "
+                                   f"{wl.n_users} users Zipf(1.1), {wl.n_requests} requests in batches of 64, LRU "
+                                   f"eviction [ADDITIONAL MEASUREMENT]", "pool_pages_per_shard": args.pool_pages,
+                       "pipeline": "the shard GPUs push batch k+1's hit prefixes while the worker GPUs push batch k's "
+                                   "stores (one host barrier over all ranks per pair); gather rows that read a page "
+                                   "being stored wait for a second barrier",
+                       "pairs_with_late_rows": r["late"]},
+            "hit_rate": r["hit_rate"], "GBps_wall": tot[1].item() / wall / 1e9,
+            "pages_per_s_device_only": tot[0].item() / (dev_ms / 1e3),
+            "GBps_device_only": tot[1].item() / (dev_ms / 1e3) / 1e9,
+            "nvlink_GBps_per_worker_device_only": tot[1].item() / n_workers / (dev_ms / 1e3) / 1e9,
+            "device_only": "slowest rank's sum over steps of the time its kernels of the step took",
+            "host_planning": ("native page directory (bikv_pm_plan_prefix_batch)" if args.c4_planner == "native"
+                              else "Python page managers with order='fast'") +
+                             ", replicated on every rank, on a host thread ahead of the kernels",
+            "gpu_launches": int(tot[2].item()),
+            "verified": {"prefixes_closed_form": verified},
+        }
+        print(json.dumps(line), flush=True)
+    dist.barrier(group=group)
+    for ptr, off in mapped:
+        N.check(lib.bikv_pool_close(C.c_void_p(ptr), off), "bikv_pool_close")
+    del shard, arenas
 
 
 # --------------------------------------------------------------------------- side measurements

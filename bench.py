@@ -46,10 +46,14 @@ def parse_args():
     ap.add_argument("--variant", default="auto", choices=["auto", "ldst", "bulk"])
     ap.add_argument("--pool-pages", type=int, default=None, help="pages per GPU (default 65536; config3: 8192)")
     ap.add_argument("--requests", type=int, default=None, help="requests per GPU (default 64; config3: 16)")
-    ap.add_argument("--workload", default="auto", choices=["auto", "config3", "config4"],
+    ap.add_argument("--host-pages", type=int, default=32768, help="spill: pages of the pinned host tier")
+    ap.add_argument("--spill-min-hits", type=int, default=1,
+                    help="spill: a prefix evicted from HBM goes to the host tier only after this many hits in HBM")
+    ap.add_argument("--workload", default="auto", choices=["auto", "config3", "config4", "spill"],
                     help="auto = configuration 1 (N = 1) or 2 (N > 1), the benchmark; config3 = long-context "
                          "geometry, requests streamed; config4 = coordinator-driven prefix reuse, N/2 shard GPUs + "
-                         "N/2 worker GPUs (both are additional measurements)")
+                         "N/2 worker GPUs; spill = prefix reuse on one GPU with an HBM tier and a pinned host tier "
+                         "(all are additional measurements)")
     ap.add_argument("--c3-order", default="longest", choices=["longest", "arrival"],
                     help="config3: stream each rank's requests longest first (balances the ranks' phases) or in arrival order")
     ap.add_argument("--c4-requests", type=int, default=20000)
@@ -678,6 +682,151 @@ def run_config4(ctx):
     del shard, arenas
 
 
+def run_spill(ctx):
+    """Side workload: the prefix-reuse stream of configuration 4 on ONE GPU whose HBM pool holds a
+    quarter of the pages (16,384) with a host tier behind it (pinned, 32,768 pages by default).
+    An item the HBM tier evicts is copied to the host tier before its pages are reused; a prefix
+    found only there is copied back and then gathered.  Reports pages/s and where the prefixes
+    were found, next to the hit rate the same HBM pool reaches with no host tier behind it.  A
+    shorter stream runs first with closed-form prefixes and checks every gathered prefix on the
+    device, whichever tier it came back from."""
+    import numpy as np
+    import torch
+
+    import bikv_b200 as B
+    from bikv_b200 import selfcheck as S
+    from bikv_b200 import workloads as W
+    from bikv_b200.coordinator import PrefixReuseWorkload
+    from bikv_b200.page_directory import PageDirectory
+    from bikv_b200.plan import build_plan
+    from bikv_b200.tiered_store import TieredPageStore
+
+    args, dev, lib = ctx["args"], ctx["dev"], ctx["lib"]
+    geom = W.GEO_B
+    hbm_pages = args.pool_pages if args.pool_pages != 65536 else 16384
+    host_pages = args.host_pages
+    mover = B.PageMover(dev, variant=ctx["variant"])
+    stream = torch.cuda.current_stream(dev)
+    arena = torch.zeros(geom.token_elems * (8192 + 256) * 64, dtype=geom.dtype, device=dev)
+    rw = geom.row_elems * geom.elt_bytes // 4
+    ok_dev = torch.ones((), dtype=torch.bool, device=dev)
+    P = geom.page_tokens
+
+    def words(off_elems, tokens):
+        n = geom.token_elems * tokens
+        return arena[off_elems:off_elems + n].view(torch.int32).view(geom.planes, tokens, rw)
+
+    def prefix_words(user, tokens):
+        return S.worker_words(geom, 0, int(user) & 0xFFFFF, tokens, 0, tokens, dev)
+
+    def run_stream(store, wl, check):
+        pages_moved = payload = 0
+        next_item = 1 << 40
+        ev = []
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for batch in wl.batches():
+            tensors = _carve(arena, geom, [r.tokens for r in batch])
+            offs = _arena_offsets(geom, [r.tokens for r in batch])
+            g_pages, g_tok, g_req, s_pages, s_tok, s_req, s_first = [], [], [], [], [], [], []
+            stored_now, hits, fills = set(), [], []
+            store.begin_batch()
+            for i, r in enumerate(batch):
+                if r.user in stored_now:
+                    pass                       # being stored by this very batch: computed again, not read
+                else:
+                    pages = store.fetch(r.user) if store.tokens_of(r.user) in (None, r.prefix_tokens) else None
+                    if pages is not None:
+                        g_pages.append(pages), g_tok.append(r.prefix_tokens), g_req.append(i)
+                        hits.append(i)
+                    else:
+                        s_pages.append(store.store(r.user, r.prefix_tokens)), s_tok.append(r.prefix_tokens)
+                        s_req.append(i), s_first.append(True)
+                        stored_now.add(r.user)
+                        fills.append(i)
+                s_pages.append(store.store(next_item, r.new_tokens, spill=False)), s_tok.append(r.new_tokens)
+                s_req.append(i), s_first.append(False)
+                next_item += 1
+            store.end_batch(stream)            # demotions, then promotions, ahead of the batch's own copies
+            gather = build_plan(g_pages, g_tok, P, item_request=g_req, n_requests=len(batch))
+            scatter = build_plan(s_pages, s_tok, P, item_request=s_req, n_requests=len(batch))
+            with_prefix = {s_req[k] for k in range(len(s_req)) if s_first[k]}
+            table = scatter.table
+            for i, r in enumerate(batch):      # a request whose prefix is not stored: new tokens sit behind it
+                if i not in with_prefix:
+                    table[table[:, 2] == i, 3] += r.prefix_tokens
+            e = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+            e[0].record(stream)
+            mover.gather(store.pool, gather, tensors)
+            if check:
+                for i in hits:
+                    r = batch[i]
+                    ok_dev.logical_and_((words(offs[i], r.tokens)[:, :r.prefix_tokens] ==
+                                         prefix_words(r.user, r.prefix_tokens)).all())
+                for i in fills:
+                    r = batch[i]
+                    words(offs[i], r.tokens)[:, :r.prefix_tokens] = prefix_words(r.user, r.prefix_tokens)
+            mover.scatter(store.pool, scatter, tensors)
+            e[1].record(stream)
+            ev.append(e)
+            pages_moved += gather.n_pages + scatter.n_pages
+            payload += (int(gather.table[:, 1].sum()) + int(scatter.table[:, 1].sum())) * geom.bytes_per_token
+        torch.cuda.synchronize()
+        wall = time.perf_counter() - t0
+        mover.check_status()
+        return dict(wall=wall, pages=pages_moved, payload=payload, batches=len(ev),
+                    dev_ms=sum(a.elapsed_time(b) for a, b in ev))
+
+    store = TieredPageStore(geom, hbm_pages, host_pages, dev, mover=mover, min_hits_to_spill=args.spill_min_hits)
+    verified = None
+    if not args.no_verify:
+        small = TieredPageStore(geom, 8192, 16384, dev, mover=mover)
+        run_stream(small, PrefixReuseWorkload(seed=1, n_workers=1, n_requests=1920, batch=64), check=True)
+        verified = bool(ok_dev.item())
+        st = small.stats
+        if not verified or st.promotions == 0 or st.demotions == 0:
+            raise SystemExit(f"bench.py spill: closed-form check failed or did not exercise both moves ({st})")
+        del small
+    launches0 = lib.bikv_launch_count()
+    wl = PrefixReuseWorkload(seed=0, n_workers=1, n_requests=args.c4_requests, batch=64)
+    r = run_stream(store, wl, check=False)
+    st = store.stats
+    # the same stream against the same HBM pool with nothing behind it (host logic only)
+    alone = PageDirectory(hbm_pages * P, P, 1, policy="lru")
+    stored, hit_alone, item = {}, 0, 1 << 40
+    for batch in wl.batches():
+        for q in batch:
+            if alone.access_item(q.user)[0] is not None and stored.get(q.user) == q.prefix_tokens:
+                hit_alone += 1
+            else:
+                alone.load_item(q.user, q.prefix_tokens)
+                stored[q.user] = q.prefix_tokens
+            alone.load_item(item, q.new_tokens)
+            item += 1
+    n = wl.n_requests
+    line = {
+        "metric": "kv_pages_per_second", "value": r["pages"] / r["wall"], "unit": "pages/s", "n_gpus": 1,
+        "steps": r["batches"], "warmup": 0, "ms_per_step": r["wall"] / r["batches"] * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "u16", "data": "synthetic",
+        "config": {"workload": f"prefix reuse on one GPU with a two-tier pool: {hbm_pages} pages in HBM, {host_pages} in "
+                               f"pinned host memory; {wl.n_users} users Zipf(1.1), {n} requests in batches of 64, LRU in "
+                               "each tier [ADDITIONAL MEASUREMENT]"},
+        "GBps_wall": r["payload"] / r["wall"] / 1e9, "pages_per_s_device_only": r["pages"] / (r["dev_ms"] / 1e3),
+        "prefixes_found": {"in_hbm": st.hbm_hits / n, "in_host_tier": st.host_hits / n,
+                           "nowhere": 1 - (st.hbm_hits + st.host_hits) / n},
+        "hit_rate": (st.hbm_hits + st.host_hits) / n, "hit_rate_same_hbm_pool_without_host_tier": hit_alone / n,
+        "tier_moves": {"demotions": st.demotions, "demotions_that_needed_no_copy": st.clean_demotions,
+                       "promotions": st.promotions, "pages_demoted": st.pages_demoted,
+                       "pages_promoted": st.pages_promoted, "dropped": st.dropped,
+                       "evictions_not_spilled": st.not_spilled,
+                       "policy": f"prefixes fetched at least {args.spill_min_hits} time(s) while in HBM are kept on "
+                                 "eviction; written-back new tokens are not"},
+        "gpu_launches": int(lib.bikv_launch_count() - launches0),
+        "verified": {"prefixes_closed_form_through_both_tiers": verified},
+    }
+    print(json.dumps(line), flush=True)
+
+
 # --------------------------------------------------------------------------- side measurements
 def peer_copy_ceilings(mover, pool, shard, rank, world, dev, barrier, total_bytes=2 << 30, reps=3):
     """What a plain contiguous copy gets out of the links right now: every rank copies one
@@ -842,7 +991,7 @@ def main():
     if args.workload != "auto":
         ctx = dict(args=args, rank=rank, world=world, dev=dev, lib=lib, variant=variant, multi=multi,
                    cpu_group=cpu_group if multi else None, local_rank=local_rank)
-        (run_config3 if args.workload == "config3" else run_config4)(ctx)
+        {"config3": run_config3, "config4": run_config4, "spill": run_spill}[args.workload](ctx)
         if multi:
             dist.barrier(group=cpu_group)
             dist.destroy_process_group()

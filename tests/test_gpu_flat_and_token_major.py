@@ -77,6 +77,7 @@ TM_GEOS = {
     "R16": KVGeometry(28, 2, 128, 16, torch.float16, TM),
     "B": KVGeometry(28, 4, 128, 16, torch.bfloat16, TM),        # 2 slabs
     "C-lite": KVGeometry(80, 8, 128, 4, torch.float16, TM),     # slabs of 64 d x 1 head
+    "C": KVGeometry(80, 8, 128, 16, torch.float16, TM),         # configuration 3's full geometry, 5 MiB pages
     "H6": KVGeometry(40, 6, 128, 4, torch.bfloat16, TM),        # slabs of 64 d x 3 heads
     "d64": KVGeometry(24, 2, 64, 16, torch.float16, TM),        # one slab per token
     "d96": KVGeometry(12, 3, 96, 5, torch.float16, TM),         # 12 d-groups: slab rows not a multiple of 8

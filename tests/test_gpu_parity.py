@@ -83,6 +83,13 @@ def test_every_tail_length(cuda, variant):
 
 
 @pytest.mark.parametrize("variant", VARIANTS)
+def test_config3_full_geometry(cuda, variant):
+    """Configuration 3 as stated: 80 layers, 8 KV heads, head 128, fp16, 16-token pages (5 MiB
+    each, 32 KiB planes), pool striped over 8 shards, ragged last pages -- against the oracle."""
+    run_case(cuda, B.GEO_C, 8, 6, 4, 11 * 16 + 5, VARIANTS[variant], seed=33, min_tokens=16 * 3 + 1)
+
+
+@pytest.mark.parametrize("variant", VARIANTS)
 def test_many_small_requests_more_items_than_grid(cuda, variant):
     run_case(cuda, B.GEO_A, 2, 2048, 64, 1024, VARIANTS[variant], seed=5, fill="normal", min_tokens=128)
 

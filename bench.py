@@ -432,7 +432,9 @@ def run_config4(ctx):
     Hazard: a prefix stored by batch k and read by batch k+1.  The planner sees it (page ids of
     the two plans intersect); those gather rows wait, on every shard, for a barrier behind the
     workers' scatters, the rest overlaps them.  Planning (all workers' shares, replicated on every
-    rank so that all hold the same page directory) runs on a host thread ahead of the kernels.
+    rank so that all hold the same page directory) runs on a host thread ahead of the kernels.  A
+    batch is planned in ONE piece and then split by worker: a user named twice in a batch, by
+    requests of two workers, is stored by the first and not read by the second.
 
     Before the timed run a shorter stream goes through the same pipeline with closed-form
     contents: every prefix a miss stores is a function of (user, token, word), and every prefix
@@ -450,7 +452,8 @@ def run_config4(ctx):
     from bikv_b200 import _native as N
     from bikv_b200 import selfcheck as S
     from bikv_b200 import workloads as W
-    from bikv_b200.coordinator import NativePrefixCacheCoordinator, PrefixCacheCoordinator, PrefixReuseWorkload
+    from bikv_b200.coordinator import (NativePrefixCacheCoordinator, PrefixCacheCoordinator, PrefixReuseWorkload,
+                                       split_by_worker)
     from bikv_b200.plan import Plan
     from bikv_b200.push import split_plans_by_owner
 
@@ -513,7 +516,7 @@ def run_config4(ctx):
         prev_written = np.zeros(0, dtype=np.int32)
         try:
             for batch in wl.batches():
-                plans = [co.plan_batch([r for r in batch if r.worker == k]) for k in range(n_workers)]
+                plans = split_by_worker(co.plan_batch(batch), n_workers)
                 late_masks = [np.isin(p.gather.table[:, 0], prev_written) for p in plans]
                 prev_written = np.concatenate([p.scatter.table[:, 0] for p in plans])
                 out_q.put((plans, late_masks, any(bool(m.any()) for m in late_masks)))
@@ -828,23 +831,21 @@ def run_spill(ctx):
 
 
 # --------------------------------------------------------------------------- side measurements
-def peer_copy_ceilings(mover, pool, shard, rank, world, dev, barrier, total_bytes=2 << 30, reps=3):
-    """What a plain contiguous copy gets out of the links right now: every rank copies one
-    slice from (pull) or to (push) every peer's shard at the same time, the slices of a rank
-    on one stream per peer, once with the copy engines (cudaMemcpyAsync: independent of this
-    library's kernels) and once with the library's flat copy kernel.  GB/s per GPU, slowest
-    rank, best of `reps` after one untimed round.  Runs before the pool is filled: the pushed
-    slices overwrite the start of every shard."""
+def peer_copy_ceilings(mover, pool, shard, rank, world, dev, barrier, nbytes=2 << 30, reps=3):
+    """What a plain contiguous copy gets out of the links right now: every rank copies one range
+    from (pull) or to (push) its right-hand neighbour's shard at the same time -- a ring, so that
+    every GPU's link carries data in both directions, as it does under the sharded pool -- once
+    with the copy engines (cudaMemcpyAsync: independent of this library's kernels) and once with
+    the library's flat copy kernel.  GB/s per GPU, slowest rank, best of `reps` after one untimed
+    round.  Runs before the pool is filled: the pushed range overwrites the start of a shard."""
     import torch
     import torch.distributed as dist
 
-    peers = [r for r in range(world) if r != rank]
-    shard_bytes = shard.numel() * shard.element_size()
-    per = min(total_bytes // len(peers), shard_bytes // world) >> 20 << 20
-    if per <= 0:
+    peer = (rank + 1) % world
+    nbytes = min(nbytes, shard.numel() * shard.element_size()) >> 20 << 20
+    if nbytes <= 0:
         return None
-    scratch = torch.empty(per * len(peers), dtype=torch.uint8, device=dev)
-    streams = [torch.cuda.Stream(dev) for _ in peers]
+    scratch = torch.empty(nbytes, dtype=torch.uint8, device=dev)
     main = torch.cuda.current_stream(dev)
 
     def run(copy, push):
@@ -854,25 +855,22 @@ def peer_copy_ceilings(mover, pool, shard, rank, world, dev, barrier, total_byte
             barrier()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record(main)
-            for i, (st, p) in enumerate(zip(streams, peers)):
-                st.wait_event(e0)
-                remote, local = pool.bases[p] + rank * per, scratch.data_ptr() + i * per
-                copy(remote if push else local, local if push else remote, per, stream=st)
-                main.wait_stream(st)
+            remote, local = pool.bases[peer], scratch.data_ptr()
+            copy(remote if push else local, local if push else remote, nbytes, stream=main)
             e1.record(main)
             main.synchronize()
             times.append(e0.elapsed_time(e1))
         t = torch.tensor([min(times[1:])], dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return per * len(peers) / (float(t[0]) / 1e3) / 1e9
+        return nbytes / (float(t[0]) / 1e3) / 1e9
 
     out = {"engine_pull_GBps_per_gpu": run(mover.copy_range_engine, False),
            "engine_push_GBps_per_gpu": run(mover.copy_range_engine, True),
            "kernel_pull_GBps_per_gpu": run(mover.copy_range, False),
            "kernel_push_GBps_per_gpu": run(mover.copy_range, True),
-           "bytes_per_gpu": per * len(peers),
-           "pattern": f"all {world} GPUs at once, each against its {len(peers)} peers, both link directions loaded; "
-                      "engine = cudaMemcpyAsync (copy engines), kernel = bikv_copy_range"}
+           "bytes_per_gpu": nbytes,
+           "pattern": f"ring over {world} GPUs, every GPU against its right-hand neighbour at once, both link "
+                      "directions loaded; engine = cudaMemcpyAsync (copy engines), kernel = bikv_copy_range"}
     torch.cuda.synchronize()
     barrier()
     del scratch

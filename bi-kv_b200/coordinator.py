@@ -203,3 +203,29 @@ class NativePrefixCacheCoordinator:
         self.misses += n - sum(hits)
         tokens = np.array([r.tokens for r in requests], dtype=np.int64)
         return BatchPlan(requests, Plan(g_store, n_g.value, tokens.copy()), Plan(s_store, n_s.value, tokens.copy()), hits)
+
+
+def split_by_worker(bp: BatchPlan, n_workers: int) -> List[BatchPlan]:
+    """One plan per worker out of a plan made for the WHOLE batch.  Planning the batch in one
+    piece matters: a user that two requests of one batch name -- on different workers -- is
+    stored by the first and, like a repeat on one worker, must not be read by the second,
+    because every gather of a batch runs before (or while) its scatters do.  Planned share by
+    share, the second request would see the entry the first one just made and count as a hit
+    on pages nobody has written yet.  Request ``i`` of worker ``k``'s share is the ``i``-th
+    request of the batch with ``worker == k``."""
+    worker_of = np.fromiter((r.worker for r in bp.requests), dtype=np.int64, count=len(bp.requests))
+    local = np.zeros(len(bp.requests), dtype=np.int32)
+    out = []
+    for k in range(n_workers):
+        idx = np.flatnonzero(worker_of == k)
+        local[idx] = np.arange(len(idx), dtype=np.int32)
+    for k in range(n_workers):
+        idx = np.flatnonzero(worker_of == k)
+        tables = []
+        for plan in (bp.gather, bp.scatter):
+            t = plan.table
+            rows = t[worker_of[t[:, 2]] == k].copy() if len(t) else t.copy()
+            rows[:, 2] = local[rows[:, 2]]
+            tables.append(Plan.from_table(rows, max(len(idx), 1)))
+        out.append(BatchPlan([bp.requests[i] for i in idx], tables[0], tables[1], [bp.hit[i] for i in idx]))
+    return out

@@ -110,3 +110,35 @@ def test_prefix_reuse_on_gpu_sampled_bit_exact(cuda):
                 checked += 1
     mover.check_status()
     assert checked > 100 and co.misses > 60, (checked, co.misses)     # evictions forced re-misses
+
+
+@pytest.mark.parametrize("native_planner", [False, True])
+def test_whole_batch_plan_split_by_worker(native, native_planner):
+    """A batch planned in one piece and split by worker: the split plans together are the whole
+    plan, and a user named by requests of two workers in ONE batch is stored once and not read
+    by the other request (its pages are written only when the batch's scatters run)."""
+    from bikv_b200.coordinator import NativePrefixCacheCoordinator, Request, split_by_worker
+    co = (NativePrefixCacheCoordinator(2, 256, 16) if native_planner
+          else PrefixCacheCoordinator(2, 256, 16, order="fast"))
+    batch = [Request(0, 7, 100, 40, 0), Request(1, 9, 50, 33, 1), Request(2, 7, 100, 20, 1),     # user 7 twice
+             Request(3, 5, 64, 32, 0), Request(4, 9, 50, 48, 0)]                                 # user 9 twice
+    bp = co.plan_batch(batch)
+    assert bp.hit == [False] * 5
+    parts = split_by_worker(bp, 2)
+    assert [len(p.requests) for p in parts] == [3, 2]
+    assert [r.request_id for r in parts[0].requests] == [0, 3, 4] and [r.request_id for r in parts[1].requests] == [1, 2]
+    assert sum(p.gather.n_pages for p in parts) == bp.gather.n_pages == 0
+    assert sum(p.scatter.n_pages for p in parts) == bp.scatter.n_pages
+    whole = sorted(map(tuple, bp.scatter.table[:, [0, 1, 3]].tolist()))
+    assert sorted(t for p in parts for t in map(tuple, p.scatter.table[:, [0, 1, 3]].tolist())) == whole
+    # worker 1's second request (user 7, stored by worker 0 in this batch) stores only its new tokens
+    s1 = parts[1].scatter.table
+    second = s1[s1[:, 2] == 1]
+    assert second[:, 1].sum() == 20 and second[0, 3] == 100
+    # the next batch finds both users: hits, gathered by whichever worker asks
+    nxt = [Request(5, 7, 100, 10, 1), Request(6, 9, 50, 10, 0)]
+    bp2 = co.plan_batch(nxt)
+    assert bp2.hit == [True, True]
+    parts2 = split_by_worker(bp2, 2)
+    assert parts2[1].gather.table[:, 1].sum() == 100 and parts2[0].gather.table[:, 1].sum() == 50
+    assert set(parts2[1].gather.table[:, 2].tolist()) == {0} and set(parts2[0].gather.table[:, 2].tolist()) == {0}

@@ -310,6 +310,7 @@ def run_config3(ctx):
 
     import bikv_b200 as B
     from bikv_b200 import _native as N
+    from bikv_b200 import multi as multi_mod
     from bikv_b200 import workloads as W
 
     args, rank, world, dev, lib, multi = (ctx[k] for k in ("args", "rank", "world", "dev", "lib", "multi"))
@@ -331,10 +332,12 @@ def run_config3(ctx):
         staged.append(mover.upload(w.plan(), geom, t))
     stream = torch.cuda.current_stream(dev)
 
+    phase_barrier = multi_mod.ShmBarrier(ctx["cpu_group"]) if multi else None
+
     def phase_end():
         if multi:
             stream.synchronize()
-            dist.barrier(group=ctx["cpu_group"])
+            phase_barrier.wait(timeout_s=300)
 
     def step(events=None):
         for i, (recs, rq) in enumerate(staged):
@@ -450,6 +453,7 @@ def run_config4(ctx):
 
     import bikv_b200 as B
     from bikv_b200 import _native as N
+    from bikv_b200 import multi as multi_mod
     from bikv_b200 import selfcheck as S
     from bikv_b200 import workloads as W
     from bikv_b200.coordinator import (NativePrefixCacheCoordinator, PrefixCacheCoordinator, PrefixReuseWorkload,
@@ -500,6 +504,7 @@ def run_config4(ctx):
                              rule=N.SHARD_BLOCK, device=dev)
     mover = B.PageMover(dev, variant=ctx["variant"])
     stream = torch.cuda.Stream(dev)
+    step_barrier = multi_mod.ShmBarrier(group)          # microseconds, where a gloo barrier costs a tenth of a step
     tables = [torch.empty((per_worker * (n_workers if is_shard else 1), 2), dtype=torch.int64).pin_memory()
               for _ in range(8)]
     rw = geom.row_elems * geom.elt_bytes // 4
@@ -604,13 +609,13 @@ def run_config4(ctx):
                 # scatter has landed
                 if not is_shard:
                     stream.synchronize()
-                dist.barrier(group=group)
+                step_barrier.wait(timeout_s=300)
                 if is_shard:
                     mover.gather_table(pool, shard_rows(plans, masks, k, late=True), table, stream=stream)
                 n_late += 1
             e1.record(stream)
             stream.synchronize()
-            dist.barrier(group=group)
+            step_barrier.wait(timeout_s=300)
             spans.append((e0, e1))
             n_steps += 1
             if check and not is_shard and cur is not None:
@@ -964,6 +969,7 @@ def main():
 
     import bikv_b200 as B
     from bikv_b200 import _native as N
+    from bikv_b200 import multi as multi_mod
     from bikv_b200 import workloads as W
     from bikv_b200.plan import build_plan
 
@@ -1130,14 +1136,18 @@ def main():
     do_g, do_s = args.only in ("both", "gather"), args.only in ("both", "scatter")
     n_dirs = int(do_g) + int(do_s)
 
+    phase_barrier = multi_mod.ShmBarrier(cpu_group) if multi else None
+
     def phase_end():
         """N > 1: ranks move data the same way at the same time (all gather, then all
         scatter), as the reference's batch-synchronous scheduler drives its workers.  A
         host barrier between phases keeps them aligned; unaligned ranks load one NVLink
-        direction with reads AND writes while the other idles."""
+        direction with reads AND writes while the other idles.  The barrier is the
+        shared-memory one: a phase lasts milliseconds and a gloo barrier over loopback TCP
+        costs a few hundred microseconds of it."""
         if multi:
             stream.synchronize()
-            barrier()
+            phase_barrier.wait(timeout_s=300)
 
     def step_resident():
         if do_g:

@@ -109,3 +109,35 @@ def test_barrier_reports_a_rank_that_left(native):
     """, timeout=90)
     assert "LEFT" in outs[1][1]
     assert "BARRIER ERROR" in outs[0][1], outs[0][1]
+
+
+def test_shared_memory_barrier_orders_ranks_and_reports_a_missing_one(native):
+    outs = _run_ranks("""
+        import time
+        b = multi.ShmBarrier()
+        # every rank sees the other's write only after the barrier
+        flag = torch.zeros(1)
+        for k in range(200):
+            b.wait(timeout_s=30)
+        t0 = time.perf_counter()
+        for k in range(2000):
+            b.wait(timeout_s=30)
+        per = (time.perf_counter() - t0) / 2000
+        print("BARRIER_US", round(per * 1e6, 1))
+        assert per < 2e-3
+        if rank == 1:
+            time.sleep(0.3)                  # rank 0 waits for a late rank, then goes on
+        b.wait(timeout_s=30)
+        if rank == 0:
+            try:
+                b.wait(timeout_s=0.5)        # rank 1 never enters this one
+                raise SystemExit("expected a timeout")
+            except RuntimeError as e:
+                assert "ranks [1]" in str(e), str(e)
+        else:
+            time.sleep(1.0)
+        b.close()
+        print("SHM_BARRIER_OK")
+    """, world=2)
+    for rc, out in outs:
+        assert rc == 0 and "SHM_BARRIER_OK" in out, out[-2000:]

@@ -337,7 +337,7 @@ def run_config3(ctx):
     def phase_end():
         if multi:
             stream.synchronize()
-            phase_barrier.wait(timeout_s=300)
+            phase_barrier.wait(timeout_s=ctx.get("barrier_timeout_s", 300))
 
     def step(events=None):
         for i, (recs, rq) in enumerate(staged):
@@ -411,10 +411,14 @@ def run_config3(ctx):
                          "nvlink_in_GBps_per_gpu": remote * payload / (g_ms / 1e3) / 1e9,
                          "nvlink_out_GBps_per_gpu": remote * payload / (s_ms / 1e3) / 1e9},
         }
-        print(json.dumps(line), flush=True)
+    else:
+        line = None
     if multi:
         dist.barrier(group=ctx["cpu_group"])
         pool.close()
+        phase_barrier.close()
+    del shard, arena
+    return line
 
 
 def run_config4(ctx):
@@ -609,13 +613,13 @@ def run_config4(ctx):
                 # scatter has landed
                 if not is_shard:
                     stream.synchronize()
-                step_barrier.wait(timeout_s=300)
+                step_barrier.wait(timeout_s=ctx.get("barrier_timeout_s", 300))
                 if is_shard:
                     mover.gather_table(pool, shard_rows(plans, masks, k, late=True), table, stream=stream)
                 n_late += 1
             e1.record(stream)
             stream.synchronize()
-            step_barrier.wait(timeout_s=300)
+            step_barrier.wait(timeout_s=ctx.get("barrier_timeout_s", 300))
             spans.append((e0, e1))
             n_steps += 1
             if check and not is_shard and cur is not None:
@@ -683,11 +687,14 @@ def run_config4(ctx):
             "gpu_launches": int(tot[2].item()),
             "verified": {"prefixes_closed_form": verified},
         }
-        print(json.dumps(line), flush=True)
+    else:
+        line = None
     dist.barrier(group=group)
     for ptr, off in mapped:
         N.check(lib.bikv_pool_close(C.c_void_p(ptr), off), "bikv_pool_close")
+    step_barrier.close()
     del shard, arenas
+    return line
 
 
 def run_spill(ctx):
@@ -832,7 +839,7 @@ def run_spill(ctx):
         "gpu_launches": int(lib.bikv_launch_count() - launches0),
         "verified": {"prefixes_closed_form_through_both_tiers": verified},
     }
-    print(json.dumps(line), flush=True)
+    return line
 
 
 # --------------------------------------------------------------------------- side measurements
@@ -944,6 +951,44 @@ def side_measure(mover, dev, geom, pool_pages, n_requests, worker_layout, steps=
     return out
 
 
+def workload_sides(args, ctx_base):
+    """Configurations 3 and 4 in a few steps each, so that every default run carries a figure
+    for them: configuration 3's geometry (80 layers x 8 KV heads x 128, fp16, 5 MiB pages) with
+    two streamed requests per GPU, and -- on an even number of GPUs -- configuration 4's
+    shard/worker pipeline over 3,200 requests, its closed-form prefix check included.  A side
+    that fails is reported as an error string; it never takes the headline down with it."""
+    rank, world = ctx_base["rank"], ctx_base["world"]
+
+    def attempt(fn, **over):
+        a = argparse.Namespace(**vars(args))
+        for k, v in over.items():
+            setattr(a, k, v)
+        try:
+            return fn(dict(ctx_base, args=a, barrier_timeout_s=60))
+        except BaseException as e:  # noqa: BLE001  (SystemExit of a failed check included)
+            return {"error": f"{type(e).__name__}: {e}"}
+
+    out = {}
+    c3 = attempt(run_config3, workload="config3", pool_pages=8192, requests=2, steps=1, warmup=1)
+    if rank == 0 and c3 is not None:
+        keep = ("value", "unit", "ms_per_step", "pages_per_s", "error")
+        out["config3_geometry_two_requests_per_gpu"] = {k: c3[k] for k in keep if k in c3}
+        if "roofline" in c3:
+            out["config3_geometry_two_requests_per_gpu"].update(
+                {k: c3["roofline"][k] for k in ("hbm_frac", "remote_fraction", "nvlink_in_GBps_per_gpu",
+                                               "nvlink_out_GBps_per_gpu", "gather_ms_per_step", "scatter_ms_per_step")},
+                workload=c3["config"]["workload"])
+    if world >= 2 and world % 2 == 0:
+        c4 = attempt(run_config4, workload="config4", c4_requests=3200)
+        if rank == 0 and c4 is not None:
+            keep = ("value", "unit", "ms_per_step", "hit_rate", "GBps_wall", "pages_per_s_device_only",
+                    "nvlink_GBps_per_worker_device_only", "verified", "error")
+            out["config4_3200_requests"] = {k: c4[k] for k in keep if k in c4}
+            if "config" in c4:
+                out["config4_3200_requests"]["workload"] = c4["config"]["workload"]
+    return out
+
+
 # --------------------------------------------------------------------------- GPU arm
 def main():
     args = parse_args()
@@ -995,7 +1040,9 @@ def main():
     if args.workload != "auto":
         ctx = dict(args=args, rank=rank, world=world, dev=dev, lib=lib, variant=variant, multi=multi,
                    cpu_group=cpu_group if multi else None, local_rank=local_rank)
-        {"config3": run_config3, "config4": run_config4, "spill": run_spill}[args.workload](ctx)
+        line = {"config3": run_config3, "config4": run_config4, "spill": run_spill}[args.workload](ctx)
+        if rank == 0 and line is not None:
+            print(json.dumps(line), flush=True)
         if multi:
             dist.barrier(group=cpu_group)
             dist.destroy_process_group()
@@ -1391,7 +1438,8 @@ def main():
         if not multi and not args.no_cpu_baseline:
             base = cpu_reference_run(20, 1, args.requests, limit_s=15.0)
             line["cpu_baseline"] = {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")}
-        print(json.dumps(line), flush=True)
+    else:
+        line = None
 
     if multi:
         barrier()
@@ -1399,6 +1447,23 @@ def main():
         if args.gather_mode == "push" and not nhd:
             for ptr, off in arena_maps:
                 N.check(lib.bikv_pool_close(C.c_void_p(ptr), off), "bikv_pool_close")
+        phase_barrier.close()
+
+    # ---- the other configurations, short, once the headline's memory has been given back ----
+    eligible = (not args.no_sides and args.geometry == "B" and args.layout == "paged" and not nhd and
+                args.only == "both" and not args.small and args.pages_from == "all")
+    if eligible:
+        shard = pool = tensors = arena = d_recs = d_reqs = d_push_recs = d_push_reqs = None   # noqa: F841
+        launch_gather = launch_scatter = None                                                 # noqa: F841
+        torch.cuda.synchronize()
+        torch.cuda.empty_cache()
+        more = workload_sides(args, dict(rank=rank, world=world, dev=dev, lib=lib, variant=variant, multi=multi,
+                                         cpu_group=cpu_group if multi else None, local_rank=local_rank))
+        if rank == 0 and more:
+            line.setdefault("side_measurements", {}).update(more)
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if multi:
         dist.destroy_process_group()
 
 

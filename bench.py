@@ -304,26 +304,40 @@ def _carve(arena, geom, tokens_list):
 def run_config3(ctx):
     """Configuration 3: long-context geometry (80 layers, 8 KV heads, head 128, fp16), requests of
     16k-32k tokens, STREAMED one at a time through a reused worker buffer (one request is up to
-    10 GiB); pool striped page_id mod N.  A step = every request gathered and scattered back."""
+    10 GiB); pool striped page_id mod N.  A step = every request gathered and scattered back.
+    On N > 1 GPUs phase i moves every rank's i-th request; the gather is pushed by the pages'
+    owners (`--gather-mode push`, the default) or pulled by the worker, the scatter is the
+    worker's push.  Before timing, the first request of every rank is gathered once from a pool
+    of closed-form contents and every word checked; the pool's position hash is compared across
+    the timed round trips."""
+    import ctypes as C
+
+    import numpy as np
     import torch
     import torch.distributed as dist
 
     import bikv_b200 as B
     from bikv_b200 import _native as N
     from bikv_b200 import multi as multi_mod
+    from bikv_b200 import selfcheck as S
     from bikv_b200 import workloads as W
+    from bikv_b200.push import split_plans_by_owner
 
     args, rank, world, dev, lib, multi = (ctx[k] for k in ("args", "rank", "world", "dev", "lib", "multi"))
     geom = W.GEO_C
     shard = B.ShardedPool.allocate_shard(geom, args.pool_pages, dev)
-    W.fill_normal_(shard, seed=99 + rank)
     pool = B.ShardedPool.exchange(shard, geom, group=ctx["cpu_group"]) if multi else B.ShardedPool.single(shard, geom)
-    reqs = W.config3(rank, world, pages_per_shard=args.pool_pages, n_requests=args.requests)
-    # Longest first on every rank: phase k then moves every rank's k-th longest request, so
-    # the ranks' phases are close in size (max/mean 1.08 instead of 1.23 in arrival order) and
-    # the barrier after each phase waits less.
-    if args.c3_order == "longest":
-        reqs.sort(key=lambda x: -x.total_tokens)
+
+    def requests_of(r):
+        out = W.config3(r, world, pages_per_shard=args.pool_pages, n_requests=args.requests)
+        # Longest first on every rank: phase k then moves every rank's k-th longest request, so
+        # the ranks' phases are close in size (max/mean 1.08 instead of 1.23 in arrival order) and
+        # the barrier after each phase waits less.
+        if args.c3_order == "longest":
+            out.sort(key=lambda x: -x.total_tokens)
+        return out
+
+    reqs = requests_of(rank)
     arena = torch.zeros(geom.token_elems * max(w.total_tokens for w in reqs), dtype=geom.dtype, device=dev)
     mover = B.PageMover(dev, variant=ctx["variant"])
     staged = []
@@ -331,6 +345,36 @@ def run_config3(ctx):
         t = _carve(arena, geom, [w.total_tokens])
         staged.append(mover.upload(w.plan(), geom, t))
     stream = torch.cuda.current_stream(dev)
+
+    # Owner-push gather: for phase i, this rank's pages of EVERY rank's i-th request go into that
+    # rank's arena (mapped here through one IPC handle per rank).
+    push = multi and args.gather_mode == "push"
+    pushed, arena_maps, pushed_remote_bytes = [], [], 0
+    if push:
+        everyone = [requests_of(r) if r != rank else reqs for r in range(world)]
+        handles = [None] * world
+        dist.all_gather_object(handles, B.ShardedPool.export_handle(arena), group=ctx["cpu_group"])
+        arena_base = []
+        for r, h in enumerate(handles):
+            if r == rank:
+                arena_base.append(arena.data_ptr())
+                continue
+            out = C.c_void_p()
+            N.check(lib.bikv_pool_import(h[0], int(h[1]), C.byref(out)), "bikv_pool_import")
+            arena_base.append(int(out.value))
+            arena_maps.append((int(out.value), int(h[1])))
+        for i in range(args.requests):
+            rows = split_plans_by_owner([everyone[r][i].plan().table for r in range(world)], [1] * world, rank,
+                                        world, args.pool_pages)
+            table = torch.tensor([[arena_base[r], everyone[r][i].total_tokens] for r in range(world)], dtype=torch.int64)
+            pushed.append((torch.from_numpy(rows).to(dev), table.to(dev)))
+            pushed_remote_bytes += int(rows[rows[:, 2] != rank, 1].sum()) * geom.bytes_per_token
+
+    def launch_gather(i):
+        if push:
+            mover.gather_dev(pool, *pushed[i])
+        else:
+            mover.gather_dev(pool, *staged[i])
 
     phase_barrier = multi_mod.ShmBarrier(ctx["cpu_group"]) if multi else None
 
@@ -343,7 +387,7 @@ def run_config3(ctx):
         for i, (recs, rq) in enumerate(staged):
             if events:
                 events[i][0].record(stream)
-            mover.gather_dev(pool, recs, rq)
+            launch_gather(i)
             if events:
                 events[i][1].record(stream)
             phase_end()
@@ -354,9 +398,33 @@ def run_config3(ctx):
                 events[i][3].record(stream)
             phase_end()
 
+    def agree(flag):
+        if not multi:
+            return bool(flag)
+        t_ok = torch.tensor([float(bool(flag))], dtype=torch.float64)
+        dist.all_reduce(t_ok, op=dist.ReduceOp.MIN)
+        return bool(t_ok[0])
+
+    # ---- the first request of every rank out of a closed-form pool, every word checked ----
+    verified = {"gather_closed_form": None, "pool_hash_unchanged": None}
+    if not args.no_verify:
+        S.fill_pool_(shard, geom, S.global_ids_of_shard(rank, world, args.pool_pages))
+        torch.cuda.synchronize()
+        phase_end()
+        launch_gather(0)
+        phase_end()
+        w0 = reqs[0]
+        tensor = _carve(arena, geom, [w0.total_tokens])[0]
+        verified["gather_closed_form"] = agree(S.check_gathered(geom, tensor, w0.page_lists[0], w0.total_tokens,
+                                                                     max_tokens_per_pass=1024))
+        if not verified["gather_closed_form"]:
+            raise SystemExit("bench.py config3: gathered words differ from what the plan implies")
+    W.fill_normal_(shard, seed=99 + rank)
+    hash_before = None if args.no_verify else S.position_hash(shard)
     sampler = ClockSampler(ctx["local_rank"]) if rank == 0 else None
     torch.cuda.synchronize()
     torch.cuda.empty_cache()      # scratch left by the pool fill; see main()
+    phase_end()
     for _ in range(args.warmup):
         step()
     torch.cuda.synchronize()
@@ -391,6 +459,14 @@ def run_config3(ctx):
     else:
         tp, tpages, tl = payload, pages, launches
     clocks = sampler.finish() if sampler else None
+    if hash_before is not None:
+        phase_end()
+        verified["pool_hash_unchanged"] = agree(S.position_hash(shard) == hash_before)
+        if not verified["pool_hash_unchanged"]:
+            raise SystemExit("bench.py config3: the pool changed across gather->scatter round trips")
+    nv_in = remote * payload / (g_ms / 1e3) / 1e9
+    if push:       # what this GPU pushed to the others per step, over the time its pushes took
+        nv_in = pushed_remote_bytes / (g_ms / 1e3) / 1e9
     if rank == 0:
         peak, peak_kind = measured_peaks()
         secs = elapsed_ms / 1e3
@@ -408,14 +484,17 @@ def run_config3(ctx):
                          "scatter_ms_per_step": s_ms, "remote_fraction": remote,
                          "hbm_achieved": 2 * payload / ((g_ms + s_ms) / 2 / 1e3) / 1e9, "hbm_peak": peak,
                          "hbm_frac": 2 * payload / ((g_ms + s_ms) / 2 / 1e3) / 1e9 / peak, "peak_kind": f"of {peak_kind}",
-                         "nvlink_in_GBps_per_gpu": remote * payload / (g_ms / 1e3) / 1e9,
+                         "nvlink_in_GBps_per_gpu": nv_in, "gather_mode": args.gather_mode if multi else None,
                          "nvlink_out_GBps_per_gpu": remote * payload / (s_ms / 1e3) / 1e9},
+            "verified": verified,
         }
     else:
         line = None
     if multi:
         dist.barrier(group=ctx["cpu_group"])
         pool.close()
+        for ptr, off in arena_maps:
+            N.check(lib.bikv_pool_close(C.c_void_p(ptr), off), "bikv_pool_close")
         phase_barrier.close()
     del shard, arena
     return line
@@ -977,7 +1056,7 @@ def workload_sides(args, ctx_base):
             out["config3_geometry_two_requests_per_gpu"].update(
                 {k: c3["roofline"][k] for k in ("hbm_frac", "remote_fraction", "nvlink_in_GBps_per_gpu",
                                                "nvlink_out_GBps_per_gpu", "gather_ms_per_step", "scatter_ms_per_step")},
-                workload=c3["config"]["workload"])
+                workload=c3["config"]["workload"], verified=c3.get("verified"))
     if world >= 2 and world % 2 == 0:
         c4 = attempt(run_config4, workload="config4", c4_requests=3200)
         if rank == 0 and c4 is not None:

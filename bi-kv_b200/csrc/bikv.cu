@@ -21,6 +21,7 @@ std::atomic<long long> g_ldst_ctas_per_sm{16};
 std::atomic<long long> g_bulk_ctas_per_sm{3};
 std::atomic<long long> g_bulk_stages{4};
 std::atomic<long long> g_seg_bytes{16384};
+std::atomic<long long> g_ldst_wide{1};     // 1: 32-byte ld/st in k_paged_ldst and k_flat where alignment allows
 std::atomic<long long> g_bulk_span{1};     // adjacent planes of a page per stage of the bulk ring
 std::atomic<long long> g_auto_variant{0};  // 0 = choose by shard count
 std::atomic<long long> g_tm_threads{0};        // CTA size of k_token_major16v; 0 = by tile size (see launcher)
@@ -410,6 +411,7 @@ int launch_paged(const bikv_pool_desc* pool, const bikv_geometry* g, const bikv_
   a.n_requests = (unsigned)n_requests;
   a.page_tokens = (unsigned)g->page_tokens;
   a.total_pages = (unsigned long long)pool->pages_per_shard * pool->n_shards;
+  a.wide = (int)g_ldst_wide.load();
   if (items == 0) return BIKV_OK;
 
   if (variant == BIKV_VARIANT_LDST) {
@@ -498,6 +500,7 @@ Knob* find_knob(const char* name) {
       {"bulk_stages", &g_bulk_stages, 2, kMaxStages},
       {"seg_bytes", &g_seg_bytes, 1024, 64 * 1024},
       {"bulk_span", &g_bulk_span, 1, 8},
+      {"ldst_wide", &g_ldst_wide, 0, 1},
       {"auto_variant", &g_auto_variant, 0, BIKV_VARIANT_BULK},
       {"ldst_threads", &g_ldst_threads, 64, 256},
       {"tm_threads", &g_tm_threads, 0, 256},
@@ -673,7 +676,10 @@ static int run_nhd(const bikv_pool_desc* pool, const bikv_geometry* geom, const 
   a.pool = to_dev(pool);
   a.planes = 2u * geom->n_layers;
   a.row_bytes = (unsigned)(geom->n_kv_heads * geom->head_dim * geom->elt_bytes);
-  a.row_vecs = a.row_bytes / 16;
+  // 32-byte accesses when the knob allows and rows are 32-byte multiples (the layer bases are
+  // checked for that alignment in the kernel); U accesses in flight per lane either way.
+  const bool wide = g_ldst_wide.load() != 0 && a.row_bytes % 32 == 0;
+  a.row_vecs = a.row_bytes / (wide ? 32 : 16);
   a.row_vecs_m = a.row_vecs == 1 ? 0u : (unsigned)((1ull << 32) / a.row_vecs + 1);
   a.plane_bytes = a.row_bytes * geom->page_tokens;
   a.page_bytes = (unsigned long long)a.plane_bytes * a.planes;
@@ -688,7 +694,10 @@ static int run_nhd(const bikv_pool_desc* pool, const bikv_geometry* geom, const 
   const int threads = 256, warps = threads / 32;
   const long long want = (items + warps - 1) / warps;
   const unsigned grid = (unsigned)std::min<long long>(want, (long long)di.sm_count * g_ldst_ctas_per_sm.load());
-  k_paged_nhd<8><<<grid, threads, 0, (cudaStream_t)stream>>>(a);
+  if (wide)
+    k_paged_nhd<4, 32><<<grid, threads, 0, (cudaStream_t)stream>>>(a);
+  else
+    k_paged_nhd<8, 16><<<grid, threads, 0, (cudaStream_t)stream>>>(a);
   return after_launch();
 }
 
@@ -776,6 +785,7 @@ int bikv_copy_pages_flat(const void* src, void* dst, const int64_t* src_off_dev,
   a.parts = (unsigned)parts;
   a.n_items = (unsigned long long)n_pages * parts;
   a.elt_bytes = (unsigned)elt_bytes;
+  a.wide = (int)g_ldst_wide.load();
   const int threads = 256, warps = threads / 32;
   const unsigned long long want = (a.n_items + warps - 1) / warps;
   unsigned grid = (unsigned)std::min<unsigned long long>(

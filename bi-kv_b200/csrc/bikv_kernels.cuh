@@ -49,6 +49,7 @@ struct PagedArgs {
   unsigned n_requests;             // bounds for the record checks below
   unsigned page_tokens;
   unsigned long long total_pages;  // n_shards * pages_per_shard
+  int wide;                        // ld/st kernel: 32-byte accesses where both sides are 32-byte aligned
   unsigned span;                   // bulk ring: adjacent planes per item (1 = one plane or part)
   unsigned groups;                 // ceil(planes / span)
 };
@@ -110,6 +111,23 @@ __device__ __forceinline__ void st_stream16(void* p, const uint4& v) {
                : "memory");
 }
 
+struct Vec32 {
+  unsigned r[8];
+};
+__device__ __forceinline__ Vec32 ld_stream32(const void* p) {
+  Vec32 v;
+  asm volatile("ld.global.L1::no_allocate.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(v.r[0]), "=r"(v.r[1]), "=r"(v.r[2]), "=r"(v.r[3]), "=r"(v.r[4]), "=r"(v.r[5]), "=r"(v.r[6]),
+                 "=r"(v.r[7])
+               : "l"(p));
+  return v;
+}
+__device__ __forceinline__ void st_stream32(void* p, const Vec32& v) {
+  asm volatile("st.global.L1::no_allocate.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "r"(v.r[0]),
+               "r"(v.r[1]), "r"(v.r[2]), "r"(v.r[3]), "r"(v.r[4]), "r"(v.r[5]), "r"(v.r[6]), "r"(v.r[7])
+               : "memory");
+}
+
 // Resolves chunk w to (pool address, worker address, byte count).  Returns
 // false for a part that lies wholly beyond the valid tokens of a partial page.
 __device__ __forceinline__ bool decode_item(const PagedArgs& a, unsigned w, char*& pool_p,
@@ -142,35 +160,59 @@ __device__ __forceinline__ bool decode_item(const PagedArgs& a, unsigned w, char
   return true;
 }
 
+// Both addresses 16-byte aligned: 16-byte accesses, U in flight per lane; with `wide` and
+// 32-byte alignment the bulk goes in 32-byte accesses (a warp instruction then covers 1 KiB).
+template <int U>
+__device__ __forceinline__ void warp_copy_aligned(const char* src, char* dst, unsigned long long bytes, int lane,
+                                                  bool wide) {
+  if (wide && (((unsigned long long)src | (unsigned long long)dst) & 31) == 0 && bytes >= 1024) {
+    constexpr int W = U / 2;
+    const unsigned long long n = bytes >> 5;
+    unsigned long long i = lane;
+    for (; i + 32ull * (W - 1) < n; i += 32ull * W) {
+      Vec32 v[W];
+#pragma unroll
+      for (int u = 0; u < W; ++u) v[u] = ld_stream32(src + ((i + 32 * u) << 5));
+#pragma unroll
+      for (int u = 0; u < W; ++u) st_stream32(dst + ((i + 32 * u) << 5), v[u]);
+    }
+    for (; i < n; i += 32) st_stream32(dst + (i << 5), ld_stream32(src + (i << 5)));
+    src += n << 5;
+    dst += n << 5;
+    bytes -= n << 5;
+  }
+  const uint4* s = reinterpret_cast<const uint4*>(src);
+  uint4* d = reinterpret_cast<uint4*>(dst);
+  const unsigned long long n = bytes >> 4;
+  unsigned long long i = lane;
+  for (; i + 32ull * (U - 1) < n; i += 32ull * U) {
+    uint4 v[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) v[u] = ld_stream16(s + i + 32 * u);
+#pragma unroll
+    for (int u = 0; u < U; ++u) st_stream16(d + i + 32 * u, v[u]);
+  }
+  for (; i < n; i += 32) st_stream16(d + i, ld_stream16(s + i));
+  for (unsigned long long b = (n << 4) + lane; b < bytes; b += 32) dst[b] = src[b];
+}
+
 // Copies `bytes` from src to dst with the 32 lanes of one warp.  Fast path:
 // both 16-byte aligned.  Otherwise the widest power-of-two unit that divides
 // both addresses is used, with a byte tail.
 template <int U>
 __device__ __forceinline__ void warp_copy(const char* src, char* dst, unsigned long long bytes,
-                                          int lane) {
+                                          int lane, bool wide = false) {
   const unsigned long long mis = (unsigned long long)src | (unsigned long long)dst;
   if ((mis & 15) == 0) {
-    const uint4* s = reinterpret_cast<const uint4*>(src);
-    uint4* d = reinterpret_cast<uint4*>(dst);
-    const unsigned long long n = bytes >> 4;
-    unsigned long long i = lane;
-    for (; i + 32ull * (U - 1) < n; i += 32ull * U) {
-      uint4 v[U];
-#pragma unroll
-      for (int u = 0; u < U; ++u) v[u] = ld_stream16(s + i + 32 * u);
-#pragma unroll
-      for (int u = 0; u < U; ++u) st_stream16(d + i + 32 * u, v[u]);
-    }
-    for (; i < n; i += 32) st_stream16(d + i, ld_stream16(s + i));
-    for (unsigned long long b = (n << 4) + lane; b < bytes; b += 32) dst[b] = src[b];
+    warp_copy_aligned<U>(src, dst, bytes, lane, wide);
     return;
   }
   if (((unsigned long long)src & 15) == ((unsigned long long)dst & 15)) {
-    // Same misalignment on both sides: peel a byte head, then the fast path.
+    // Same misalignment on both sides: peel a byte head, then the aligned path.
     unsigned long long head = 16 - ((unsigned long long)src & 15);
     if (head > bytes) head = bytes;
     for (unsigned long long b = lane; b < head; b += 32) dst[b] = src[b];
-    if (bytes > head) warp_copy<U>(src + head, dst + head, bytes - head, lane);
+    if (bytes > head) warp_copy_aligned<U>(src + head, dst + head, bytes - head, lane, wide);
     return;
   }
   if ((mis & 7) == 0) {
@@ -207,9 +249,9 @@ __global__ void __launch_bounds__(256) k_paged_ldst(const __grid_constant__ Page
     unsigned bytes;
     if (!decode_item(a, w, pool_p, work_p, bytes)) continue;
     if (a.to_pool)
-      warp_copy<U>(work_p, pool_p, bytes, lane);
+      warp_copy<U>(work_p, pool_p, bytes, lane, a.wide != 0);
     else
-      warp_copy<U>(pool_p, work_p, bytes, lane);
+      warp_copy<U>(pool_p, work_p, bytes, lane, a.wide != 0);
   }
 }
 
@@ -226,7 +268,7 @@ struct NhdArgs {
   unsigned n_items;        // n_pages * planes
   unsigned planes;
   unsigned row_bytes;
-  unsigned row_vecs;       // row_bytes / 16
+  unsigned row_vecs;       // row_bytes / bytes per access (16 or 32)
   unsigned row_vecs_m;     // multiply-high constant for division by row_vecs (0 when 1)
   unsigned plane_bytes;
   unsigned long long page_bytes;
@@ -237,8 +279,25 @@ struct NhdArgs {
   long long slots_per_layer;
 };
 
-template <int U>
+// VB = bytes per access: 16, or 32 when rows and bases are 32-byte aligned.
+template <int VB>
+struct NhdVec;
+template <>
+struct NhdVec<16> {
+  using T = uint4;
+  static __device__ __forceinline__ T ld(const char* p) { return ld_stream16(p); }
+  static __device__ __forceinline__ void st(char* p, const T& v) { st_stream16(p, v); }
+};
+template <>
+struct NhdVec<32> {
+  using T = Vec32;
+  static __device__ __forceinline__ T ld(const char* p) { return ld_stream32(p); }
+  static __device__ __forceinline__ void st(char* p, const T& v) { st_stream32(p, v); }
+};
+
+template <int U, int VB>
 __global__ void __launch_bounds__(256) k_paged_nhd(const __grid_constant__ NhdArgs a) {
+  using V = NhdVec<VB>;
   const unsigned lane = threadIdx.x & 31;
   const unsigned warps_per_cta = blockDim.x >> 5;
   const unsigned stride = gridDim.x * warps_per_cta;
@@ -263,35 +322,46 @@ __global__ void __launch_bounds__(256) k_paged_nhd(const __grid_constant__ NhdAr
       shard = (unsigned)(id / a.pool.pages_per_shard);
       local = id % a.pool.pages_per_shard;
     }
-    uint4* pool_p = reinterpret_cast<uint4*>(a.pool.base[shard] + local * a.page_bytes +
-                                             (unsigned long long)plane * a.plane_bytes);
+    char* pool_p = a.pool.base[shard] + local * a.page_bytes + (unsigned long long)plane * a.plane_bytes;
     const unsigned kv = plane & 1;
-    char* layer_base = reinterpret_cast<char*>(layer_addr);
-    uint4* work_p = reinterpret_cast<uint4*>(layer_base + ((unsigned long long)r.w * 2 + kv) * a.row_bytes);
-    const unsigned n = r.y * a.row_vecs;
-    auto wi = [&](unsigned i) {   // worker-side vector index of pool-side vector i
+    char* work_p = reinterpret_cast<char*>(layer_addr) + ((unsigned long long)r.w * 2 + kv) * a.row_bytes;
+    if (VB == 32 && (layer_addr & 31)) {
+      // A layer tensor aligned to 16 but not to 32 bytes in a launch sized for 32-byte accesses:
+      // this plane goes in 16-byte accesses (rare; not worth a tuned loop).
+      const unsigned rv = a.row_vecs * 2, n16 = r.y * rv;
+      for (unsigned i = lane; i < n16; i += 32) {
+        const unsigned long long wofs = (unsigned long long)(i + (i / rv) * rv) * 16;
+        if (!a.to_pool)
+          st_stream16(work_p + wofs, ld_stream16(pool_p + (unsigned long long)i * 16));
+        else
+          st_stream16(pool_p + (unsigned long long)i * 16, ld_stream16(work_p + wofs));
+      }
+      continue;
+    }
+    const unsigned n = r.y * a.row_vecs;          // accesses of VB bytes in the valid rows
+    auto wo = [&](unsigned i) -> unsigned long long {   // worker-side byte offset of pool-side access i
       const unsigned t = a.row_vecs_m ? __umulhi(i, a.row_vecs_m) : i;
-      return i + t * a.row_vecs;  // t*2*row_vecs + (i - t*row_vecs)
+      return (unsigned long long)(i + t * a.row_vecs) * VB;  // t*2*row_vecs + (i - t*row_vecs)
     };
     unsigned i = lane;
     if (!a.to_pool) {
       for (; i + 32u * (U - 1) < n; i += 32u * U) {
-        uint4 v[U];
+        typename V::T v[U];
 #pragma unroll
-        for (int u = 0; u < U; ++u) v[u] = ld_stream16(pool_p + i + 32 * u);
+        for (int u = 0; u < U; ++u) v[u] = V::ld(pool_p + (unsigned long long)(i + 32 * u) * VB);
 #pragma unroll
-        for (int u = 0; u < U; ++u) st_stream16(work_p + wi(i + 32 * u), v[u]);
+        for (int u = 0; u < U; ++u) V::st(work_p + wo(i + 32 * u), v[u]);
       }
-      for (; i < n; i += 32) st_stream16(work_p + wi(i), ld_stream16(pool_p + i));
+      for (; i < n; i += 32) V::st(work_p + wo(i), V::ld(pool_p + (unsigned long long)i * VB));
     } else {
       for (; i + 32u * (U - 1) < n; i += 32u * U) {
-        uint4 v[U];
+        typename V::T v[U];
 #pragma unroll
-        for (int u = 0; u < U; ++u) v[u] = ld_stream16(work_p + wi(i + 32 * u));
+        for (int u = 0; u < U; ++u) v[u] = V::ld(work_p + wo(i + 32 * u));
 #pragma unroll
-        for (int u = 0; u < U; ++u) st_stream16(pool_p + i + 32 * u, v[u]);
+        for (int u = 0; u < U; ++u) V::st(pool_p + (unsigned long long)(i + 32 * u) * VB, v[u]);
       }
-      for (; i < n; i += 32) st_stream16(pool_p + i, ld_stream16(work_p + wi(i)));
+      for (; i < n; i += 32) V::st(pool_p + (unsigned long long)i * VB, V::ld(work_p + wo(i)));
     }
   }
 }
@@ -520,6 +590,7 @@ struct FlatArgs {
   unsigned parts;
   unsigned seg_bytes;
   unsigned elt_bytes;
+  int wide;
 };
 
 template <int U>
@@ -537,7 +608,7 @@ __global__ void __launch_bounds__(256) k_flat(const __grid_constant__ FlatArgs a
     const long long so = a.src_off ? __ldg(a.src_off + page) : 0;
     const long long dn = a.dst_off ? __ldg(a.dst_off + page) : 0;
     warp_copy<U>(a.src + so * (long long)a.elt_bytes + off, a.dst + dn * (long long)a.elt_bytes + off,
-                 bytes, lane);
+                 bytes, lane, a.wide != 0);
   }
 }
 

@@ -173,3 +173,34 @@ def test_paged_worker_bad_layer_bases_are_skipped(cuda):
         with pytest.raises(B.BikvError) as e:
             mover.check_status()
         assert e.value.status == want
+
+
+def test_paged_worker_layers_aligned_to_16_but_not_32_bytes(cuda):
+    """With 32-byte accesses switched on (the default) a layer tensor that starts on a 16-byte
+    boundary only is still served, in 16-byte accesses."""
+    g = GEOS["small"]
+    shards_cpu = make_shards(g, 1, 12, 6)
+    shard = shards_cpu[0].to(cuda)
+    pool = B.ShardedPool.single(shard, g)
+    mover = B.PageMover(cuda)
+    slots = 48
+    row = 2 * g.n_kv_heads * g.head_dim
+    backing = [torch.zeros(slots * row + 8, dtype=g.dtype, device=cuda) for _ in range(g.n_layers)]
+    layers = [b[8:].view(slots, 2, g.n_kv_heads, g.head_dim) for b in backing]        # +16 bytes
+    assert all(t.data_ptr() % 32 == 16 for t in layers)
+    plan = Plan.from_table(np.array([[3, 16, 0, 16], [7, 5, 0, 0], [1, 16, 0, 32]]), 1)
+    recs = [tuple(r) for r in plan.table.tolist()]
+    mover.gather_nhd(pool, plan, layers)
+    torch.cuda.synchronize()
+    ref = [torch.zeros(slots, 2, g.n_kv_heads, g.head_dim, dtype=g.dtype) for _ in range(g.n_layers)]
+    O.gather_nhd(shards_cpu, g, recs, ref)
+    for a, b in zip(layers, ref):
+        assert equal_bits(a, b)
+    fresh = [normal((slots, 2, g.n_kv_heads, g.head_dim), g.dtype, 90 + l) for l in range(g.n_layers)]
+    for t, f in zip(layers, fresh):
+        t.copy_(f.to(cuda))
+    mover.scatter_nhd(pool, plan, layers)
+    torch.cuda.synchronize()
+    O.scatter_nhd(shards_cpu, g, recs, fresh)
+    assert equal_bits(shard, shards_cpu[0])
+    mover.check_status()

@@ -401,6 +401,28 @@ def test_bad_request_bases_in_a_device_table_are_skipped_not_dereferenced(cuda, 
         assert e.value.status == want
 
 
+def test_ldst_kernels_with_32_byte_accesses(cuda, native):
+    """`ldst_wide`: 32-byte loads and stores wherever both sides are 32-byte aligned, 16-byte
+    ones and byte tails elsewhere (rows of 16 bytes, odd tails, unaligned flat copies)."""
+    old = native.bikv_get_tuning(b"ldst_wide")
+    try:
+        assert native.bikv_set_tuning(b"ldst_wide", 1) == 0
+        for name, pages in (("tiny", 48), ("small", 48), ("A", 48), ("B", 48), ("C-lite", 32), ("u8", 48), ("f32", 48)):
+            g = GEOS[name]
+            run_case(cuda, g, 2, pages // 2, 5, 9 * g.page_tokens, N.VARIANT_LDST, seed=len(name))
+        for tail in (1, 7, 15):
+            run_case(cuda, SMALL, 1, 8, 1, 16 + tail, N.VARIANT_LDST, seed=tail, min_tokens=16 + tail)
+        mover = B.PageMover(cuda)
+        src = torch.arange(1 << 20, dtype=torch.int32, device=cuda).view(torch.uint8)
+        for so, do, n in ((0, 0, 1 << 20), (32, 64, 100_000), (16, 48, 77_777), (3, 3, 65_537), (1, 2, 4099)):
+            dst = torch.zeros(1 << 21, dtype=torch.uint8, device=cuda)
+            mover.copy_range(dst.data_ptr() + do, src.data_ptr() + so, n)
+            torch.cuda.synchronize()
+            assert torch.equal(dst[do:do + n], src[so:so + n]) and int(dst[:do].sum()) == 0 and int(dst[do + n:].sum()) == 0
+    finally:
+        native.bikv_set_tuning(b"ldst_wide", old)
+
+
 @pytest.mark.parametrize("span", [2, 3, 4, 8])
 def test_bulk_ring_with_several_planes_per_stage(cuda, native, span):
     """The bulk ring may move `bulk_span` adjacent planes of a page per stage (one load

@@ -96,6 +96,8 @@ SIGNATURES = {
         [_P, C.c_int64, _P, C.c_int32, C.POINTER(PoolDesc), C.POINTER(Geometry), C.c_int],
     ),
     "bikv_check_worker_base": (C.c_int, [_P]),
+    "bikv_plan_split_by_owner": (C.c_int64, [_P, _P, _P, C.c_int32, C.c_int32, C.c_int32, C.c_int64, C.c_int32, _P,
+                                             C.c_int64]),
     "bikv_gather": (
         C.c_int,
         [C.POINTER(PoolDesc), C.POINTER(Geometry), _P, C.c_int64, _P, C.c_int32, C.c_int, _P, _P],
@@ -192,13 +194,17 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if not force and not _stale():
         return LIB_PATH
     nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
-    cmd = [nvcc, *NVCC_FLAGS, "-I", INCLUDE, "-o", LIB_PATH]
+    tmp = LIB_PATH + f".{os.getpid()}.tmp"        # built aside, then moved into place in one step
+    cmd = [nvcc, *NVCC_FLAGS, "-I", INCLUDE, "-o", tmp]
     if verbose:
         cmd += ["-Xptxas", "-v"]
     cmd += [os.path.join(CSRC, s) for s in SOURCES]
     res = subprocess.run(cmd, capture_output=True, text=True)
     if res.returncode != 0:
+        if os.path.exists(tmp):
+            os.unlink(tmp)
         raise RuntimeError(f"nvcc failed:\n{res.stdout}\n{res.stderr}")
+    os.replace(tmp, LIB_PATH)
     if verbose:
         print(res.stderr)
     return LIB_PATH

@@ -600,6 +600,59 @@ int64_t bikv_plan_build(const int32_t* pages_flat, const int64_t* item_page_begi
   return n;
 }
 
+int64_t bikv_plan_split_by_owner(const bikv_page_rec* const* tables, const int64_t* n_rows,
+                                 const int32_t* requests_per_worker, int32_t n_workers, int32_t owner,
+                                 int32_t n_shards, int64_t pages_per_shard, int32_t shard_rule,
+                                 bikv_page_rec* out, int64_t out_capacity) {
+  if (n_workers < 0 || n_shards <= 0 || owner < 0 || owner >= n_shards || pages_per_shard <= 0 || out_capacity < 0)
+    return BIKV_ERR_BAD_ARG;
+  if (shard_rule != BIKV_SHARD_MOD && shard_rule != BIKV_SHARD_BLOCK) return BIKV_ERR_BAD_ARG;
+  if (n_workers == 0) return 0;
+  if (!tables || !n_rows || !requests_per_worker || (!out && out_capacity > 0)) return BIKV_ERR_BAD_ARG;
+  // Pass 1: this owner's rows per worker.  Pass 2: merge the workers' sequences by the
+  // position (i + 1/2) / n of a row within its worker's n rows, ties to the lower worker, so
+  // that the destinations interleave in proportion and a worker's rows keep their order.
+  std::vector<std::vector<int64_t>> mine((size_t)n_workers);
+  int64_t total = 0;
+  for (int32_t w = 0; w < n_workers; ++w) {
+    if (n_rows[w] < 0 || (n_rows[w] > 0 && !tables[w])) return BIKV_ERR_BAD_ARG;
+    for (int64_t i = 0; i < n_rows[w]; ++i) {
+      const int64_t id = tables[w][i].page_id;
+      if (id < 0) return BIKV_ERR_PAGE_RANGE;
+      const int64_t shard = shard_rule == BIKV_SHARD_MOD ? id % n_shards : id / pages_per_shard;
+      if (shard >= n_shards) return BIKV_ERR_PAGE_RANGE;
+      if (shard == owner) mine[(size_t)w].push_back(i);
+    }
+    total += (int64_t)mine[(size_t)w].size();
+  }
+  if (total > out_capacity) return BIKV_ERR_TOO_LARGE;
+  std::vector<int64_t> base((size_t)n_workers, 0), at((size_t)n_workers, 0);
+  for (int32_t w = 1; w < n_workers; ++w) {
+    if (requests_per_worker[w - 1] < 0) return BIKV_ERR_BAD_ARG;
+    base[(size_t)w] = base[(size_t)w - 1] + requests_per_worker[w - 1];
+  }
+  for (int64_t k = 0; k < total; ++k) {
+    int32_t best = -1;
+    for (int32_t w = 0; w < n_workers; ++w) {
+      const int64_t n = (int64_t)mine[(size_t)w].size();
+      if (at[(size_t)w] >= n) continue;
+      if (best < 0) {
+        best = w;
+        continue;
+      }
+      // (2*at_w + 1) / n_w  <  (2*at_b + 1) / n_b   compared without division
+      const int64_t nb = (int64_t)mine[(size_t)best].size();
+      if ((__int128)(2 * at[(size_t)w] + 1) * nb < (__int128)(2 * at[(size_t)best] + 1) * n) best = w;
+    }
+    bikv_page_rec r = tables[best][mine[(size_t)best][(size_t)at[(size_t)best]++]];
+    const int64_t req = (int64_t)r.request + base[(size_t)best];
+    if (r.request < 0 || r.request >= requests_per_worker[best] || req > 0x7fffffffll) return BIKV_ERR_BAD_ARG;
+    r.request = (int32_t)req;
+    out[k] = r;
+  }
+  return total;
+}
+
 int bikv_check_worker_base(const void* base) {
   return worker_base_status((unsigned long long)(uintptr_t)base);
 }

@@ -20,12 +20,12 @@ pulled gather, which is the local phase plus the remote phase laid end to end).
 """
 from __future__ import annotations
 
-from typing import List, Sequence
+import ctypes as C
+from typing import Sequence
 
 import numpy as np
 
 from . import _native as N
-from .pool import shard_of
 
 
 def split_plans_by_owner(tables: Sequence[np.ndarray], requests_per_worker: Sequence[int], owner: int,
@@ -35,19 +35,21 @@ def split_plans_by_owner(tables: Sequence[np.ndarray], requests_per_worker: Sequ
     table over all workers: worker ``r``'s request ``i`` becomes ``sum(requests_per_worker[:r]) + i``.
     Row order: the workers' rows are interleaved in proportion to their counts (row ``i`` of a
     worker with ``n`` rows sorts at ``(i + 1/2) / n``), plan order kept inside a worker, so that
-    at any moment of the sweep the kernel writes to all destinations at once."""
-    out: List[np.ndarray] = []
-    keys: List[np.ndarray] = []
-    base = 0
-    for r, table in enumerate(tables):
-        t = np.asarray(table, dtype=np.int32).reshape(-1, 4)
-        shard, _ = shard_of(t[:, 0].astype(np.int64), n_shards, pages_per_shard, rule)
-        mine = t[shard == owner].copy()
-        mine[:, 2] += base
-        out.append(mine)
-        keys.append((np.arange(len(mine), dtype=np.float64) + 0.5) / max(len(mine), 1))
-        base += int(requests_per_worker[r])
-    if not out:
+    at any moment of the sweep the kernel writes to all destinations at once.  The work is done
+    by ``bikv_plan_split_by_owner`` (native, host only)."""
+    ts = [np.ascontiguousarray(t, dtype=np.int32).reshape(-1, 4) for t in tables]
+    n = len(ts)
+    if n == 0:
         return np.zeros((0, 4), dtype=np.int32)
-    rows = np.concatenate(out)
-    return np.ascontiguousarray(rows[np.argsort(np.concatenate(keys), kind="stable")])
+    ptrs = (C.c_void_p * n)(*[t.ctypes.data for t in ts])
+    rows = np.array([len(t) for t in ts], dtype=np.int64)
+    reqs = np.ascontiguousarray(requests_per_worker, dtype=np.int32)
+    if len(reqs) != n:
+        raise ValueError("requests_per_worker and tables differ in length")
+    out = np.empty((int(rows.sum()), 4), dtype=np.int32)
+    got = N.lib().bikv_plan_split_by_owner(ptrs, rows.ctypes.data_as(C.c_void_p), reqs.ctypes.data_as(C.c_void_p), n,
+                                           int(owner), int(n_shards), int(pages_per_shard), int(rule),
+                                           out.ctypes.data_as(C.c_void_p), len(out))
+    if got < 0:
+        raise N.BikvError(int(got), "bikv_plan_split_by_owner")
+    return out[:got]

@@ -155,6 +155,27 @@ int bikv_plan_validate(const bikv_page_rec* recs, int64_t n_pages,
                        int check_overlap);
 
 /*
+ * The shard-driven SEND: in the reference the KVCache shard is the active side of a
+ * gather and writes into the worker's buffer (KVCache.send_data_batch -> post_rdma_write,
+ * DistributedStorage/kvcache.py:96-113).  Here the GPU that owns a page may do the same
+ * with bikv_gather, given a plan that holds only ITS pages and a request table whose
+ * bases are the workers' tensors as mapped on that GPU.  This builds that plan: from
+ * every worker's records it keeps those whose page lives on shard `owner` and renumbers
+ * `request` into one table over all workers (worker w's request i becomes
+ * requests_per_worker[0] + ... + requests_per_worker[w-1] + i).  Rows of different
+ * workers are interleaved in proportion to their counts (a worker's own order is kept):
+ * a kernel sweeps its plan front to back with all CTAs side by side, so rows grouped by
+ * destination would send every owner's traffic to one worker at a time.
+ *   tables[w], n_rows[w]   worker w's records (host memory)
+ * Returns the number of records written, or a negative status (BIKV_ERR_TOO_LARGE when
+ * `out_capacity` is too small; the sum of n_rows always suffices).
+ */
+int64_t bikv_plan_split_by_owner(const bikv_page_rec* const* tables, const int64_t* n_rows,
+                                 const int32_t* requests_per_worker, int32_t n_workers, int32_t owner,
+                                 int32_t n_shards, int64_t pages_per_shard, int32_t shard_rule,
+                                 bikv_page_rec* out, int64_t out_capacity);
+
+/*
  * The rule every kernel applies to a worker-side base address -- a request's KV
  * tensor (bikv_request_desc.base) or a layer tensor of a paged worker cache --
  * before it forms an address from it: BIKV_ERR_BAD_ARG for NULL,

@@ -48,6 +48,27 @@ def test_worker_base_rule(native):
         assert f(C.c_void_p(0x7F0000000000 + off)) == N.ERR_ALIGNMENT, off
 
 
+def test_owner_split_through_the_c_abi(native):
+    import ctypes as C
+    t0 = np.array([[0, 16, 0, 0], [1, 16, 0, 16], [2, 16, 1, 0], [4, 5, 1, 16]], dtype=np.int32)
+    t1 = np.array([[6, 16, 0, 0], [3, 16, 0, 16]], dtype=np.int32)
+    ptrs = (C.c_void_p * 2)(t0.ctypes.data, t1.ctypes.data)
+    rows = np.array([4, 2], dtype=np.int64)
+    reqs = np.array([2, 1], dtype=np.int32)
+    out = np.zeros((6, 4), dtype=np.int32)
+    call = lambda owner, cap=6, rule=N.SHARD_MOD, shards=2: native.bikv_plan_split_by_owner(
+        ptrs, rows.ctypes.data_as(C.c_void_p), reqs.ctypes.data_as(C.c_void_p), 2, owner, shards, 8, rule,
+        out.ctypes.data_as(C.c_void_p), cap)
+    assert call(0) == 4                    # pages 0, 2, 4 of worker 0 and page 6 of worker 1
+    assert sorted(out[:4, 0].tolist()) == [0, 2, 4, 6]
+    assert out[out[:, 0] == 6][0].tolist() == [6, 16, 2, 0]           # worker 1's request 0 -> 2
+    assert [r for r in out[:4, 0].tolist() if r != 6] == [0, 2, 4]    # worker 0's order kept
+    assert call(1) == 2 and sorted(out[:2, 0].tolist()) == [1, 3]
+    assert call(0, cap=3) == N.ERR_TOO_LARGE
+    assert call(2) == N.ERR_BAD_ARG and call(0, shards=0) == N.ERR_BAD_ARG and call(0, rule=7) == N.ERR_BAD_ARG
+    assert call(0, rule=N.SHARD_BLOCK) == 6 and call(1, rule=N.SHARD_BLOCK) == 0     # every id < pages_per_shard
+
+
 def test_tuning_knobs(native):
     assert native.bikv_set_tuning(b"nope", 1) == N.ERR_BAD_ARG
     old = native.bikv_get_tuning(b"bulk_stages")

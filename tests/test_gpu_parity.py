@@ -440,6 +440,38 @@ def test_bulk_ring_with_several_planes_per_stage(cuda, native, span):
         native.bikv_set_tuning(b"bulk_span", old)
 
 
+def test_request_tables_are_reused_only_for_the_same_live_tensors(cuda):
+    """A serving loop hands the mover the same KV tensors again and again: their request
+    table is built once.  New tensors -- even at recycled addresses or object ids -- get a
+    new one."""
+    g = SMALL
+    shards_cpu = make_shards(g, 1, 24, 4)
+    pool = B.ShardedPool.single(shards_cpu[0].to(cuda), g)
+    mover = B.PageMover(cuda)
+    plan = build_plan([[3, 9], [5]], [30, 16], g.page_tokens, item_request=[0, 1], n_requests=2)
+    recs = [tuple(r) for r in plan.table.tolist()]
+    want = make_workers(g, [30, 16])
+    O.gather(shards_cpu, g, recs, want)
+    out = make_workers(g, [30, 16], cuda)
+    first = mover.request_table(g, out).clone()
+    kept = mover.request_table(g, out)
+    assert mover.request_table(g, out) is kept and torch.equal(kept, first)      # the same objects: the kept table
+    assert not torch.equal(mover.request_table(g, list(reversed(out))), first)
+    for _ in range(3):
+        for t in out:
+            t.zero_()
+        mover.gather(pool, plan, out)
+        torch.cuda.synchronize()
+        assert all(equal_bits(a, b) for a, b in zip(out, want))
+    for _ in range(5):                                              # fresh tensors each time, old ones dropped
+        out = make_workers(g, [30, 16], cuda)
+        mover.gather(pool, plan, out)
+        torch.cuda.synchronize()
+        assert all(equal_bits(a, b) for a, b in zip(out, want))
+        del out
+    mover.check_status()
+
+
 def test_one_mover_shared_by_threads_on_their_own_streams(cuda):
     """The reference serves its data methods from a 20-thread gRPC pool
     (distributed_grpc_init.py:127,144).  Eight threads share one PageMover, each on its own

@@ -871,16 +871,16 @@ def run_spill(ctx):
         return dict(wall=wall, pages=pages_moved, payload=payload, batches=len(ev),
                     dev_ms=sum(a.elapsed_time(b) for a, b in ev))
 
-    store = TieredPageStore(geom, hbm_pages, host_pages, dev, mover=mover, min_hits_to_spill=args.spill_min_hits)
     verified = None
     if not args.no_verify:
-        small = TieredPageStore(geom, 8192, 16384, dev, mover=mover)
+        small = TieredPageStore(geom, 8192, min(16384, host_pages), dev, mover=mover)
         run_stream(small, PrefixReuseWorkload(seed=1, n_workers=1, n_requests=1920, batch=64), check=True)
         verified = bool(ok_dev.item())
         st = small.stats
         if not verified or st.promotions == 0 or st.demotions == 0:
             raise SystemExit(f"bench.py spill: closed-form check failed or did not exercise both moves ({st})")
         del small
+    store = TieredPageStore(geom, hbm_pages, host_pages, dev, mover=mover, min_hits_to_spill=args.spill_min_hits)
     launches0 = lib.bikv_launch_count()
     wl = PrefixReuseWorkload(seed=0, n_workers=1, n_requests=args.c4_requests, batch=64)
     r = run_stream(store, wl, check=False)
@@ -1031,8 +1031,8 @@ def side_measure(mover, dev, geom, pool_pages, n_requests, worker_layout, steps=
 
 
 def workload_sides(args, ctx_base):
-    """Configurations 3 and 4 in a few steps each, so that every default run carries a figure
-    for them: configuration 3's geometry (80 layers x 8 KV heads x 128, fp16, 5 MiB pages) with
+    """Configurations 3 and 4 (and, on one GPU, the two-tier pool) in a few steps each, so that
+    every default run carries a figure for them: configuration 3's geometry (80 layers x 8 KV heads x 128, fp16, 5 MiB pages) with
     two streamed requests per GPU, and -- on an even number of GPUs -- configuration 4's
     shard/worker pipeline over 3,200 requests, its closed-form prefix check included.  A side
     that fails is reported as an error string; it never takes the headline down with it."""
@@ -1057,6 +1057,14 @@ def workload_sides(args, ctx_base):
                 {k: c3["roofline"][k] for k in ("hbm_frac", "remote_fraction", "nvlink_in_GBps_per_gpu",
                                                "nvlink_out_GBps_per_gpu", "gather_ms_per_step", "scatter_ms_per_step")},
                 workload=c3["config"]["workload"], verified=c3.get("verified"))
+    if world == 1:
+        sp = attempt(run_spill, workload="spill", pool_pages=8192, host_pages=8192, c4_requests=3200)
+        if sp is not None:
+            keep = ("value", "unit", "hit_rate", "hit_rate_same_hbm_pool_without_host_tier", "prefixes_found",
+                    "tier_moves", "verified", "error")
+            out["host_tier_3200_requests"] = {k: sp[k] for k in keep if k in sp}
+            if "config" in sp:
+                out["host_tier_3200_requests"]["workload"] = sp["config"]["workload"]
     if world >= 2 and world % 2 == 0:
         c4 = attempt(run_config4, workload="config4", c4_requests=3200)
         if rank == 0 and c4 is not None:

@@ -68,3 +68,18 @@ def test_reference_arm_says_what_it_ran_and_leaves_the_cuda_library_alone():
     assert line["config"]["requests"] == 2 and "BOUNDED SAMPLE" in line["config"]["workload"]
     assert line["cpu_baseline"]["kind"] == "port" and line["e2e"]["h2d_bytes_per_step"] == 0
     assert "LIBBIKV_MAPPED False" in res.stdout
+
+
+def test_a_failing_side_measurement_is_reported_not_raised(monkeypatch):
+    """The short runs of the other configurations must never take the headline down: without a
+    CUDA device each of them fails, and each failure comes back as an error string."""
+    if torch.cuda.is_available():
+        return
+    bench = _bench()
+    monkeypatch.setattr(sys, "argv", ["bench.py"])
+    args = bench.parse_args()
+    args.pool_pages, args.requests = 65536, 64
+    out = bench.workload_sides(args, dict(rank=0, world=1, dev=torch.device("cuda:0"), lib=None, variant=0,
+                                          multi=False, cpu_group=None, local_rank=0))
+    assert set(out) == {"config3_geometry_two_requests_per_gpu", "host_tier_3200_requests"}
+    assert all("error" in v and isinstance(v["error"], str) for v in out.values())

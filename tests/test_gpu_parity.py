@@ -97,12 +97,13 @@ def test_many_small_requests_more_items_than_grid(cuda, variant):
 @pytest.mark.parametrize("seg", [1024, 4096, 16384, 65536])
 @pytest.mark.parametrize("variant", VARIANTS)
 def test_segment_sizes(cuda, native, variant, seg):
-    old = native.bikv_get_tuning(b"seg_bytes")
+    old = native.bikv_get_tuning(b"seg_bytes"), native.bikv_get_tuning(b"ldst_seg_bytes")
     try:
-        assert native.bikv_set_tuning(b"seg_bytes", seg) == 0
+        assert native.bikv_set_tuning(b"seg_bytes", seg) == 0 and native.bikv_set_tuning(b"ldst_seg_bytes", seg) == 0
         run_case(cuda, GEOS["C-lite"], 1, 32, 3, 100, VARIANTS[variant], seed=seg)
     finally:
-        native.bikv_set_tuning(b"seg_bytes", old)
+        native.bikv_set_tuning(b"seg_bytes", old[0])
+        native.bikv_set_tuning(b"ldst_seg_bytes", old[1])
 
 
 @pytest.mark.parametrize("stages", [2, 3, 8, 12])

@@ -38,7 +38,8 @@ std::atomic<long long> g_tm_split_tile_kib{96};  // the same for a slab that spl
 std::atomic<long long> g_tm_scatter_staged{1};  // k_token_major16v scatter: 1 = through staged worker rows, 0 = through the transposed tile
 std::atomic<long long> g_tm_gather_stages{0};   // buffers in the gather's cp.async ring of k_token_major16v: 2, 3, 0 = by tile size
 std::atomic<long long> g_tm_scatter_stages{2};  // the same for the staged scatter
-std::atomic<long long> g_tm_max_heads{64};     // cap on heads per slab when the slab splits the heads
+std::atomic<long long> g_tm_max_heads{64};
+std::atomic<long long> g_tm_single{1};         // k_token_major16v: 1 = one item per CTA, no ring (0 = persistent CTAs with a cp.async ring)     // cap on heads per slab when the slab splits the heads
 
 int cuda_fail(cudaError_t e) {
   tl_cuda_error = (int)e;
@@ -182,8 +183,7 @@ int launch_token_major16(const bikv_pool_desc* pool, const bikv_geometry* g, con
   if ((unsigned long long)items * std::max<unsigned>(a.slabs, (unsigned)g->page_tokens) >= (1ull << 32) ||
       (unsigned long long)(Gs * 8ull * H * L) * std::max(L, H * Gs) >= (1ull << 32))
     return BIKV_ERR_TOO_LARGE;
-  const long long per_sm = std::max<long long>(1, std::min<long long>(8, (220 * 1024) / (smem + 1024)));
-  const unsigned grid = (unsigned)std::min<long long>(items, (long long)di.sm_count * per_sm);
+  const unsigned grid = (unsigned)items;      // one item per CTA: the block scheduler balances the launch
   if (grid == 0) return BIKV_OK;
   if (smem > 40 * 1024)
     BIKV_CUDA(cudaFuncSetAttribute(k_token_major16, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -236,7 +236,8 @@ int launch_token_major16v(const bikv_pool_desc* pool, const bikv_geometry* g, co
   if (stages == 0) stages = tile <= 48 * 1024 ? 3 : 2;
   if (stages < 2) stages = 2;
   if (stages * unit > di.max_optin_smem) stages = 2;
-  const long long smem = (to_pool && !staged) ? tile : stages * unit;
+  const bool single = g_tm_single.load() != 0 && !(to_pool && !staged);
+  const long long smem = (to_pool && !staged) ? tile : (single ? unit : stages * unit);
   if (smem > di.max_optin_smem) return 1;
   const unsigned slabs = (G / Gs) * (H / Hs);
   const long long items = n_pages * g->page_tokens * (long long)slabs;
@@ -276,7 +277,8 @@ int launch_token_major16v(const bikv_pool_desc* pool, const bikv_geometry* g, co
   a.n_requests = (unsigned)n_requests;
   a.total_pages = (unsigned long long)pool->pages_per_shard * pool->n_shards;
   const long long per_sm = std::max<long long>(1, std::min<long long>(12, (220 * 1024) / (smem + 1024)));
-  const unsigned grid = (unsigned)std::min<long long>(items, (long long)di.sm_count * per_sm);
+  a.single = single ? 1 : 0;
+  const unsigned grid = single ? (unsigned)items : (unsigned)std::min<long long>(items, (long long)di.sm_count * per_sm);
   if (grid == 0) return BIKV_OK;
   const int mode = staged ? 2 : (to_pool ? 1 : 0);
   const bool ring3 = mode != 1 && stages == 3;
@@ -300,7 +302,13 @@ int launch_token_major16v(const bikv_pool_desc* pool, const bikv_geometry* g, co
   // 96 KiB tiles (80 layers x 8 heads): gather 0.912 / 0.923 / 0.916 with 128 / 192 / 256;
   // staged scatter 0.916 / 0.963 / 0.970 / 0.957 with 128 / 192 / 224 / 256; the scatter
   // through the transposed tile 0.753 / 0.766 / 0.786 with 128 / 192 / 256.
+  // One item per CTA (the default): 0.98-0.99 / 1.01 gather / scatter for 28 layers x 2 or 4 heads and 1.00 / 1.00
+  // for 80 layers x 8 heads, against 0.92-0.94 / 0.93-0.98 for the persistent ring -- the CTAs that share an
+  // SM cover each other's latencies and the block scheduler balances the launch.  Gather with 128 or 64 threads
+  // 0.984-0.990, with 256 0.78; scatter with 64 threads 1.007, with 256 0.87.
   unsigned threads = (unsigned)g_tm_threads.load();
+  if (threads == 0 && single)
+    threads = to_pool ? (tile <= 48 * 1024 ? 64 : 224) : (tile <= 48 * 1024 ? 128 : 192);
   if (threads == 0) {
     if (to_pool)
       threads = staged ? (tile <= 48 * 1024 ? 64 : 224) : (tile <= 48 * 1024 ? 128 : 256);
@@ -364,8 +372,7 @@ int launch_token_major(const bikv_pool_desc* pool, const bikv_geometry* g, const
   a.n_requests = (unsigned)n_requests;
   a.total_pages = (unsigned long long)pool->pages_per_shard * pool->n_shards;
   const int threads = 256;
-  int per_sm = (int)std::max<long long>(1, std::min<long long>(8, (200 * 1024) / std::max<long long>(smem, 1)));
-  unsigned grid = (unsigned)std::min<long long>(items, (long long)di.sm_count * per_sm);
+  unsigned grid = (unsigned)items;            // one item per CTA
   if (grid == 0) return BIKV_OK;
   auto launch = [&](auto kern) -> int {
     if (smem > 48 * 1024)
@@ -516,6 +523,7 @@ Knob* find_knob(const char* name) {
       {"tm_tile_kib", &g_tm_tile_kib, 8, 100},
       {"tm_split_tile_kib", &g_tm_split_tile_kib, 8, 100},
       {"tm_max_heads", &g_tm_max_heads, 1, 64},
+      {"tm_single", &g_tm_single, 0, 1},
       {"tm_scatter_staged", &g_tm_scatter_staged, 0, 1},
       {"tm_gather_stages", &g_tm_gather_stages, 0, 3},
       {"tm_scatter_stages", &g_tm_scatter_stages, 0, 3},

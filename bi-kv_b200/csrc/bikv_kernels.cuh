@@ -921,6 +921,7 @@ struct TokenMajor16vArgs {
   unsigned LU;           // L / 4: 16-byte units per row
   unsigned RU;           // padded row pitch in units, a multiple of 8
   unsigned d_skip;       // (H - Hs) * LU: pool units between the runs of consecutive d
+  int single;            // 1: one item per CTA, no ring (the grid is then as large as the work)
   FastDiv div_LU, div_Hs, div_HG, div_Gs, div_slabs, div_hslabs, div_ptok;
   unsigned long long token_bytes;  // D*H*L*4
   int to_pool;
@@ -1043,6 +1044,18 @@ __global__ void __launch_bounds__(256) k_token_major16v(const __grid_constant__ 
         }
       }
     };
+    if (a.single) {
+      // One item per CTA: load, wait, write out, exit.  The CTAs that share an SM cover each
+      // other's latencies and the block scheduler hands out the items.
+      const TmItem it = tm16v_item<SPLIT>(a, blockIdx.x);
+      if (!it.valid) return;
+      load(it, tm16v_tile);
+      cp_async_commit();
+      cp_async_wait_all();
+      __syncthreads();
+      emit(it, tm16v_tile);
+      return;
+    }
     unsigned w = blockIdx.x;
     if constexpr (RING3) {
       // Three tiles: the slabs of the next two items are in flight while the current one
@@ -1145,6 +1158,18 @@ __global__ void __launch_bounds__(256) k_token_major16v(const __grid_constant__ 
         }
       }
     };
+    if (a.single) {
+      // One item per CTA: load, wait, write out, exit.  The CTAs that share an SM cover each
+      // other's latencies and the block scheduler hands out the items.
+      const TmItem it = tm16v_item<SPLIT>(a, blockIdx.x);
+      if (!it.valid) return;
+      load(it, tm16v_tile);
+      cp_async_commit();
+      cp_async_wait_all();
+      __syncthreads();
+      emit(it, tm16v_tile);
+      return;
+    }
     unsigned w = blockIdx.x;
     if constexpr (RING3) {   // the worker vectors of the next two items in flight
       TmItem cur = tm16v_item<SPLIT>(a, w);

@@ -112,7 +112,7 @@ int bikv_last_cuda_error(void);
 /* Number of kernels this library has launched in this process. */
 int64_t bikv_launch_count(void);
 /* Tuning knobs: "ldst_ctas_per_sm", "bulk_ctas_per_sm", "bulk_stages", "bulk_span", "ldst_wide",
- * "ldst_seg_bytes",
+ * "ldst_seg_bytes", "tm_single",
  * "seg_bytes", "auto_variant", "ldst_threads", "tm_threads", "tm16_threads", "tm_max_groups",
  * "tm_tile_kib", "tm_split_tile_kib", "tm_max_heads", "tm_scatter_staged", "tm_gather_stages",
  * "tm_scatter_stages".

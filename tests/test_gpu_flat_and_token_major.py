@@ -88,9 +88,19 @@ TM_GEOS = {
 }
 
 
+@pytest.fixture(params=[1, 0], ids=["one_item_per_cta", "persistent_ring"])
+def tm_mode(request, native):
+    """Both forms of the 16-byte-unit kernel: one item per CTA (the default) and persistent CTAs
+    with a cp.async ring."""
+    old = native.bikv_get_tuning(b"tm_single")
+    assert native.bikv_set_tuning(b"tm_single", request.param) == 0
+    yield request.param
+    native.bikv_set_tuning(b"tm_single", old)
+
+
 @pytest.mark.parametrize("geo", TM_GEOS)
 @pytest.mark.parametrize("n_shards", [1, 3])
-def test_token_major_gather_scatter(cuda, geo, n_shards):
+def test_token_major_gather_scatter(cuda, geo, n_shards, tm_mode):
     g = TM_GEOS[geo]
     rng = np.random.default_rng(len(geo) + n_shards)
     per = 6
@@ -118,7 +128,7 @@ def test_token_major_gather_scatter(cuda, geo, n_shards):
 @pytest.mark.parametrize("staged", [0, 1])
 @pytest.mark.parametrize("tile_kib,split_kib,threads", [(8, 8, 0), (8, 16, 64), (16, 32, 96), (100, 100, 256), (48, 96, 0)])
 @pytest.mark.parametrize("geo", ["R16", "R50", "B", "H6", "C-lite", "d96"])
-def test_token_major_slab_shapes(cuda, native, geo, tile_kib, split_kib, threads, staged):
+def test_token_major_slab_shapes(cuda, native, geo, tile_kib, split_kib, threads, staged, tm_mode):
     """The slab of the 16-byte transposing kernel (d-groups x heads) follows the tile caps;
     every shape, CTA size and scatter mode moves the same bytes."""
     g = TM_GEOS[geo]

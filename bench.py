@@ -585,7 +585,9 @@ def run_config4(ctx):
     else:
         pool = B.ShardedPool([open_handle(handles[s][0]) for s in range(n_shards)], args.pool_pages, geom,
                              rule=N.SHARD_BLOCK, device=dev)
-    mover = B.PageMover(dev, variant=ctx["variant"])
+    # Launches here are short (a batch moves about 1.5 GB per worker): the ld/st kernel, which has no
+    # ring to fill and drain, measured 1.58-1.63 M pages/s on 2 + 2 GPUs against 1.51-1.55 M for the bulk ring.
+    mover = B.PageMover(dev, variant=N.VARIANT_LDST if args.variant == "auto" else ctx["variant"])
     stream = torch.cuda.Stream(dev)
     step_barrier = multi_mod.ShmBarrier(group)          # microseconds, where a gloo barrier costs a tenth of a step
     tables = [torch.empty((per_worker * (n_workers if is_shard else 1), 2), dtype=torch.int64).pin_memory()

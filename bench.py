@@ -1320,13 +1320,14 @@ def main():
         from bikv_b200 import selfcheck as S
         return S.position_hash(shard)
 
+    # nvidia-smi takes a few hundred ms to deliver its first sample: start it well ahead of the timed steps
+    sampler = ClockSampler(local_rank) if rank == 0 else None
     checksum_before = shard_checksum() if args.only == "both" and not args.no_verify else None
     # Give back the scratch blocks that filling and checksumming the pool left in torch's
     # caching allocator: with them still mapped the copy kernels measured 2 % slower
     # (0.970 against 0.988 of the HBM copy peak, same box, back to back).
     torch.cuda.synchronize()
     torch.cuda.empty_cache()
-    sampler = ClockSampler(local_rank) if rank == 0 else None
     for _ in range(args.warmup):
         step_resident()
     torch.cuda.synchronize()

@@ -57,6 +57,9 @@ def parse_args():
     ap.add_argument("--c3-order", default="longest", choices=["longest", "arrival"],
                     help="config3: stream each rank's requests longest first (balances the ranks' phases) or in arrival order")
     ap.add_argument("--c4-requests", type=int, default=20000)
+    ap.add_argument("--c4-placement", default="item", choices=["item", "striped"],
+                    help="config 4: 'item' = an item's pages live on ONE shard, chosen by the multi-shard page manager as "
+                         "in the reference; 'striped' = one page directory over all shards, page id mod shards")
     ap.add_argument("--c4-planner", default="native", choices=["native", "python"],
                     help="config4: page directory in C++ (bikv_pm_*) or the Python page managers (order='fast')")
     ap.add_argument("--geometry", default="B", choices=["A", "B", "C", "R"],
@@ -577,14 +580,20 @@ def run_config4(ctx):
         mapped.append((int(out.value), int(h[1])))
         return int(out.value)
 
+    # Placement.  'item': the multi-shard page manager puts an item on one shard (global page id =
+    # shard * pages + page), as ``DistributedStorage/PageManager.py:164-203`` does.  'striped': one
+    # directory over all shards' pages and page id mod shards names the shard, so every item -- the
+    # most popular users' prefixes too -- is served by all shards alike.
+    striped = args.c4_placement == "striped"
+    rule = N.SHARD_MOD if striped else N.SHARD_BLOCK
     if is_shard:
         # the pool as this shard addresses it: only its own pages are ever named in its plans
-        pool = B.ShardedPool([shard.data_ptr()] * n_shards, args.pool_pages, geom, rule=N.SHARD_BLOCK, device=dev,
+        pool = B.ShardedPool([shard.data_ptr()] * n_shards, args.pool_pages, geom, rule=rule, device=dev,
                              keepalive=[shard])
         arena_base = [[open_handle(h) for h in handles[n_shards + w]] for w in range(n_workers)]
     else:
         pool = B.ShardedPool([open_handle(handles[s][0]) for s in range(n_shards)], args.pool_pages, geom,
-                             rule=N.SHARD_BLOCK, device=dev)
+                             rule=rule, device=dev)
     # Launches here are short (a batch moves about 1.5 GB per worker): the ld/st kernel, which has no
     # ring to fill and drain, measured 1.58-1.63 M pages/s on 2 + 2 GPUs against 1.51-1.55 M for the bulk ring.
     mover = B.PageMover(dev, variant=N.VARIANT_LDST if args.variant == "auto" else ctx["variant"])
@@ -596,9 +605,10 @@ def run_config4(ctx):
     ok_dev = torch.ones((), dtype=torch.bool, device=dev)
 
     def make_coordinator():
-        return (NativePrefixCacheCoordinator(n_shards, args.pool_pages, geom.page_tokens)
+        dirs, pages = (1, n_shards * args.pool_pages) if striped else (n_shards, args.pool_pages)
+        return (NativePrefixCacheCoordinator(dirs, pages, geom.page_tokens)
                 if args.c4_planner == "native"
-                else PrefixCacheCoordinator(n_shards, args.pool_pages, geom.page_tokens, order="fast"))
+                else PrefixCacheCoordinator(dirs, pages, geom.page_tokens, order="fast"))
 
     def planner(wl, co, out_q):
         """Every worker's share of every batch, and which gather rows read a page the batch before
@@ -626,58 +636,73 @@ def run_config4(ctx):
         ones), destinations interleaved, and the request table of the workers' arenas."""
         tabs = [p.gather.table[m if late else ~m] for p, m in zip(plans, masks)]
         nreq = [len(p.requests) for p in plans]
-        rows = split_plans_by_owner(tabs, nreq, me, n_shards, args.pool_pages, rule=N.SHARD_BLOCK)
+        rows = split_plans_by_owner(tabs, nreq, me, n_shards, args.pool_pages, rule=rule)
         return Plan.from_table(rows, sum(nreq), transient=True)
 
     def run_stream(wl, co, check):
         q = queue.Queue(maxsize=3)
         th = threading.Thread(target=planner, args=(wl, co, q), daemon=True)
         th.start()
-        pages = payload = n_steps = n_late = 0
+        pages = payload = n_steps = n_late = pushed = 0
         spans = []
         launches0 = lib.bikv_launch_count()
         torch.cuda.synchronize()
         dist.barrier(group=group)
         t0 = time.perf_counter()
+        bpt = geom.bytes_per_token
+
+        def prepare(item, k):
+            """Host work of step k: the request table of the arenas it writes and, on a shard, this
+            shard's rows.  Runs while step k-1's kernels do."""
+            if item is None:
+                return None
+            plans, masks, has_late = item
+            table = tables[k % len(tables)]
+            st = {"has_late": has_late}
+            if is_shard:
+                tn, at = table.numpy(), 0
+                for w, p in enumerate(plans):
+                    offs = np.asarray(_arena_offsets(geom, p.tokens), dtype=np.int64)
+                    tn[at:at + len(offs), 0] = arena_base[w][k % 2] + offs * geom.elt_bytes
+                    tn[at:at + len(offs), 1] = p.tokens
+                    at += len(offs)
+                st["table"] = table[:at]
+                st["early"] = shard_rows(plans, masks, k, late=False)
+                st["late"] = shard_rows(plans, masks, k, late=True) if has_late else None
+                st["cur"] = True
+            else:
+                bp = plans[me]
+                offs = _arena_offsets(geom, bp.tokens)
+                table = table[:len(bp.tokens)]
+                tn = table.numpy()
+                tn[:, 0] = arenas[k % 2].data_ptr() + np.asarray(offs, dtype=np.int64) * geom.elt_bytes
+                tn[:, 1] = bp.tokens
+                st["cur"] = (bp, k % 2, table, offs)
+                g = bp.gather.table
+                st["pages"] = len(g) + bp.scatter.n_pages
+                st["payload"] = (int(g[:, 1].sum()) + int(bp.scatter.table[:, 1].sum())) * bpt
+            return st
+
         prev = None          # worker: (share, arena index, table, offsets) whose scatter is due
         k = 0
-        drained = False
+        nxt = prepare(q.get(), 0)
+        drained = nxt is None
         while True:
-            item = None if drained else q.get()
-            drained = item is None
-            if drained and prev is None:
+            st = nxt
+            if st is None and prev is None:
                 break
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record(stream)
-            has_late = False
-            cur = None
-            if item is not None:
-                plans, masks, has_late = item
-                table = tables[k % len(tables)]
-                if is_shard:
-                    tn, at = table.numpy(), 0
-                    for w, p in enumerate(plans):
-                        offs = np.asarray(_arena_offsets(geom, p.tokens), dtype=np.int64)
-                        tn[at:at + len(offs), 0] = arena_base[w][k % 2] + offs * geom.elt_bytes
-                        tn[at:at + len(offs), 1] = p.tokens
-                        at += len(offs)
-                    table = table[:at]
-                    cur = True
-                else:
-                    bp = plans[me]
-                    offs = _arena_offsets(geom, bp.tokens)
-                    table = table[:len(bp.tokens)]
-                    tn = table.numpy()
-                    tn[:, 0] = arenas[k % 2].data_ptr() + np.asarray(offs, dtype=np.int64) * geom.elt_bytes
-                    tn[:, 1] = bp.tokens
-                    cur = (bp, k % 2, table, offs)
-                    g = bp.gather.table
-                    pages += len(g) + bp.scatter.n_pages
-                    payload += (int(g[:, 1].sum()) + int(bp.scatter.table[:, 1].sum())) * geom.bytes_per_token
+            has_late = st is not None and st["has_late"]
+            cur = st["cur"] if st is not None else None
+            if st is not None and not is_shard:
+                pages += st["pages"]
+                payload += st["payload"]
             # -- the stores of this step --
             if is_shard:
-                if item is not None:
-                    mover.gather_table(pool, shard_rows(plans, masks, k, late=False), table, stream=stream)
+                if st is not None:
+                    pushed += int(st["early"].table[:, 1].sum()) * bpt
+                    mover.gather_table(pool, st["early"], st["table"], stream=stream)
             elif prev is not None:
                 pbp, pa, ptable, poffs = prev
                 if check:
@@ -688,7 +713,14 @@ def run_config4(ctx):
                             if i in stored and not pbp.hit[i]:
                                 words(arenas[pa], poffs[i], r.tokens)[:, :r.prefix_tokens] = \
                                     prefix_words(r.user, r.prefix_tokens)
+                pushed += int(pbp.scatter.table[:, 1].sum()) * bpt
                 mover.scatter_table(pool, pbp.scatter, ptable, stream=stream)
+            # -- while they run: the host work of the next step --
+            if drained:
+                nxt = None
+            else:
+                nxt = prepare(q.get(), k + 1)
+                drained = nxt is None
             if has_late:
                 # rows that read what the workers are writing right now: once every worker's
                 # scatter has landed
@@ -696,7 +728,8 @@ def run_config4(ctx):
                     stream.synchronize()
                 step_barrier.wait(timeout_s=ctx.get("barrier_timeout_s", 300))
                 if is_shard:
-                    mover.gather_table(pool, shard_rows(plans, masks, k, late=True), table, stream=stream)
+                    pushed += int(st["late"].table[:, 1].sum()) * bpt
+                    mover.gather_table(pool, st["late"], st["table"], stream=stream)
                 n_late += 1
             e1.record(stream)
             stream.synchronize()
@@ -713,9 +746,7 @@ def run_config4(ctx):
                         if cbp.hit[i]:
                             got = words(arenas[ca], coffs[i], r.tokens)[:, :r.prefix_tokens]
                             ok_dev.logical_and_((got == prefix_words(r.user, r.prefix_tokens)).all())
-            prev = cur if not is_shard else (True if item is not None else None)
-            if is_shard and drained:
-                prev = None
+            prev = cur if not is_shard else (True if st is not None else None)
             k += 1
         torch.cuda.synchronize()
         wall = time.perf_counter() - t0
@@ -723,7 +754,7 @@ def run_config4(ctx):
         mover.check_status()
         dev_ms = sum(a.elapsed_time(b) for a, b in spans)
         return dict(wall=wall, dev_ms=dev_ms, pages=pages, payload=payload, steps=n_steps, late=n_late,
-                    launches=lib.bikv_launch_count() - launches0, hit_rate=co.hit_rate)
+                    launches=lib.bikv_launch_count() - launches0, hit_rate=co.hit_rate, pushed=pushed)
 
     # ---- closed-form pass over a shorter stream (same pipeline, contents checked) ----
     verified = None
@@ -744,6 +775,8 @@ def run_config4(ctx):
     dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
     tot = torch.tensor([float(r["pages"]), float(r["payload"]), float(r["launches"])], dtype=torch.float64)
     dist.all_reduce(tot, op=dist.ReduceOp.SUM, group=group)
+    per_rank = [None] * world
+    dist.all_gather_object(per_rank, (r["dev_ms"], r["pushed"]), group=group)
     if rank == 0:
         wall, dev_ms = t.tolist()
         line = {
@@ -753,6 +786,8 @@ def run_config4(ctx):
             "config": {"workload": f"config4: {n_shards} shard GPUs + {n_workers} worker GPUs, config-1 geometry, "
                                    f"{wl.n_users} users Zipf(1.1), {wl.n_requests} requests in batches of 64, LRU "
                                    f"eviction [ADDITIONAL MEASUREMENT]", "pool_pages_per_shard": args.pool_pages,
+                       "placement": ("striped: one page directory over all shards, page id mod shards" if striped else
+                                     "item: an item's pages on one shard, chosen by the multi-shard page manager"),
                        "pipeline": "the shard GPUs push batch k+1's hit prefixes while the worker GPUs push batch k's "
                                    "stores (one host barrier over all ranks per pair); gather rows that read a page "
                                    "being stored wait for a second barrier",
@@ -767,6 +802,11 @@ def run_config4(ctx):
                              ", replicated on every rank, on a host thread ahead of the kernels",
             "gpu_launches": int(tot[2].item()),
             "verified": {"prefixes_closed_form": verified},
+            # who is busy: an item lives on one shard, so the shard that holds the most popular users pushes most
+            "per_rank": {"role": ["shard"] * n_shards + ["worker"] * n_workers,
+                         "GB_pushed": [round(b / 1e9, 2) for _, b in per_rank],
+                         "kernel_ms_per_step": [round(ms / r["steps"], 3) for ms, _ in per_rank],
+                         "GBps_while_its_kernels_ran": [round(b / 1e6 / ms, 1) if ms else None for ms, b in per_rank]},
         }
     else:
         line = None

@@ -606,20 +606,24 @@ def run_config4(ctx):
 
     def make_coordinator():
         dirs, pages = (1, n_shards * args.pool_pages) if striped else (n_shards, args.pool_pages)
-        return (NativePrefixCacheCoordinator(dirs, pages, geom.page_tokens)
+        return (NativePrefixCacheCoordinator(dirs, pages, geom.page_tokens, transient_plans=True)
                 if args.c4_planner == "native"
                 else PrefixCacheCoordinator(dirs, pages, geom.page_tokens, order="fast"))
 
     def planner(wl, co, out_q):
         """Every worker's share of every batch, and which gather rows read a page the batch before
         writes (decided over ALL workers, so every rank decides alike)."""
+        being_written = np.zeros(n_shards * args.pool_pages, dtype=bool)     # by the batch before
         prev_written = np.zeros(0, dtype=np.int32)
         try:
             for batch in wl.batches():
-                plans = split_by_worker(co.plan_batch(batch), n_workers)
-                late_masks = [np.isin(p.gather.table[:, 0], prev_written) for p in plans]
-                prev_written = np.concatenate([p.scatter.table[:, 0] for p in plans])
-                out_q.put((plans, late_masks, any(bool(m.any()) for m in late_masks)))
+                bp = co.plan_batch(batch)
+                late = being_written[bp.gather.table[:, 0]]
+                being_written[prev_written] = False
+                prev_written = bp.scatter.table[:, 0].copy()
+                being_written[prev_written] = True
+                plans, late_masks = split_by_worker(bp, n_workers, gather_flags=late, transient=True)
+                out_q.put((plans, late_masks, bool(late.any())))
         finally:
             out_q.put(None)
 
@@ -715,6 +719,8 @@ def run_config4(ctx):
                                     prefix_words(r.user, r.prefix_tokens)
                 pushed += int(pbp.scatter.table[:, 1].sum()) * bpt
                 mover.scatter_table(pool, pbp.scatter, ptable, stream=stream)
+            if not has_late:
+                e1.record(stream)
             # -- while they run: the host work of the next step --
             if drained:
                 nxt = None
@@ -731,7 +737,7 @@ def run_config4(ctx):
                     pushed += int(st["late"].table[:, 1].sum()) * bpt
                     mover.gather_table(pool, st["late"], st["table"], stream=stream)
                 n_late += 1
-            e1.record(stream)
+                e1.record(stream)
             stream.synchronize()
             step_barrier.wait(timeout_s=ctx.get("barrier_timeout_s", 300))
             spans.append((e0, e1))

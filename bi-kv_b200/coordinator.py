@@ -20,7 +20,7 @@ from __future__ import annotations
 import ctypes as C
 import random
 from dataclasses import dataclass
-from typing import Iterator, List, Tuple
+from typing import Iterator, List, Optional, Tuple
 
 import numpy as np
 
@@ -166,8 +166,13 @@ class NativePrefixCacheCoordinator:
     batch instead of a Python loop over requests (LRU policy, smallest-free-page allocation:
     the decisions of ``PrefixCacheCoordinator(order="fast", rng=XorShiftChoice(seed))``)."""
 
-    def __init__(self, n_shards: int, pages_per_shard: int, page_tokens: int, seed: int = 0):
+    def __init__(self, n_shards: int, pages_per_shard: int, page_tokens: int, seed: int = 0,
+                 transient_plans: bool = False):
+        """``transient_plans``: the plans of a batch hand their pinned buffers back when the batch
+        plan is dropped (a caller that keeps ``table`` views beyond that must leave it off)."""
         from .page_directory import PageDirectory
+
+        self.transient_plans = bool(transient_plans)
 
         self.n_shards, self.pages_per_shard, self.page_tokens = n_shards, pages_per_shard, page_tokens
         self.pm = PageDirectory(pages_per_shard * page_tokens, page_tokens, n_shards, policy="lru", seed=seed)
@@ -202,30 +207,60 @@ class NativePrefixCacheCoordinator:
         self.hits += sum(hits)
         self.misses += n - sum(hits)
         tokens = np.array([r.tokens for r in requests], dtype=np.int64)
-        return BatchPlan(requests, Plan(g_store, n_g.value, tokens.copy()), Plan(s_store, n_s.value, tokens.copy()), hits)
+        tr = self.transient_plans
+        return BatchPlan(requests, Plan(g_store, n_g.value, tokens.copy(), tr), Plan(s_store, n_s.value, tokens.copy(), tr),
+                         hits)
 
 
-def split_by_worker(bp: BatchPlan, n_workers: int) -> List[BatchPlan]:
+def split_by_worker(bp: BatchPlan, n_workers: int, gather_flags: Optional[np.ndarray] = None,
+                    transient: bool = False):
     """One plan per worker out of a plan made for the WHOLE batch.  Planning the batch in one
     piece matters: a user that two requests of one batch name -- on different workers -- is
     stored by the first and, like a repeat on one worker, must not be read by the second,
     because every gather of a batch runs before (or while) its scatters do.  Planned share by
     share, the second request would see the entry the first one just made and count as a hit
     on pages nobody has written yet.  Request ``i`` of worker ``k``'s share is the ``i``-th
-    request of the batch with ``worker == k``."""
-    worker_of = np.fromiter((r.worker for r in bp.requests), dtype=np.int64, count=len(bp.requests))
-    local = np.zeros(len(bp.requests), dtype=np.int32)
+    request of the batch with ``worker == k``; rows keep their order within a worker.
+
+    ``gather_flags`` (one value per row of ``bp.gather``) is split alongside: the call then
+    returns ``(plans, flags_per_worker)``.  ``transient``: the plans hand their pinned buffers
+    back for reuse when they are dropped, so no ``table`` view of them may be kept beyond that."""
+    from .plan import _pinned_i32
+
+    n = len(bp.requests)
+    worker_of = np.fromiter((r.worker for r in bp.requests), dtype=np.int64, count=n)
+    tokens = np.fromiter((r.tokens for r in bp.requests), dtype=np.int64, count=n)
+    by_worker = np.argsort(worker_of, kind="stable")
+    n_req = np.bincount(worker_of, minlength=n_workers)
+    first_req = np.concatenate(([0], np.cumsum(n_req)))
+    local = np.empty(n, dtype=np.int32)
+    local[by_worker] = np.arange(n, dtype=np.int32) - np.repeat(first_req[:-1], n_req).astype(np.int32)
+
+    def split(plan: Plan, flags=None):
+        t = plan.table
+        w_rows = worker_of[t[:, 2]] if len(t) else np.zeros(0, dtype=np.int64)
+        order = np.argsort(w_rows, kind="stable")
+        rows = t[order]
+        if len(rows):
+            rows[:, 2] = local[rows[:, 2]]
+        first = np.concatenate(([0], np.cumsum(np.bincount(w_rows, minlength=n_workers))))
+        plans = []
+        for k in range(n_workers):
+            part = rows[first[k]:first[k + 1]]
+            store = _pinned_i32(len(part), 4)
+            store.numpy()[:len(part)] = part
+            req_tokens = tokens[by_worker[first_req[k]:first_req[k + 1]]]
+            plans.append(Plan(store, len(part), req_tokens if len(req_tokens) else np.zeros(1, dtype=np.int64),
+                              transient))
+        if flags is None:
+            return plans, None
+        f = np.asarray(flags)[order]
+        return plans, [f[first[k]:first[k + 1]] for k in range(n_workers)]
+
+    gathers, flags = split(bp.gather, gather_flags)
+    scatters, _ = split(bp.scatter)
     out = []
     for k in range(n_workers):
-        idx = np.flatnonzero(worker_of == k)
-        local[idx] = np.arange(len(idx), dtype=np.int32)
-    for k in range(n_workers):
-        idx = np.flatnonzero(worker_of == k)
-        tables = []
-        for plan in (bp.gather, bp.scatter):
-            t = plan.table
-            rows = t[worker_of[t[:, 2]] == k].copy() if len(t) else t.copy()
-            rows[:, 2] = local[rows[:, 2]]
-            tables.append(Plan.from_table(rows, max(len(idx), 1)))
-        out.append(BatchPlan([bp.requests[i] for i in idx], tables[0], tables[1], [bp.hit[i] for i in idx]))
-    return out
+        idx = by_worker[first_req[k]:first_req[k + 1]]
+        out.append(BatchPlan([bp.requests[i] for i in idx], gathers[k], scatters[k], [bp.hit[i] for i in idx]))
+    return out if gather_flags is None else (out, flags)

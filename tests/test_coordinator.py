@@ -142,3 +142,28 @@ def test_whole_batch_plan_split_by_worker(native, native_planner):
     parts2 = split_by_worker(bp2, 2)
     assert parts2[1].gather.table[:, 1].sum() == 100 and parts2[0].gather.table[:, 1].sum() == 50
     assert set(parts2[1].gather.table[:, 2].tolist()) == {0} and set(parts2[0].gather.table[:, 2].tolist()) == {0}
+
+
+def test_split_by_worker_keeps_row_order_and_splits_row_flags(native):
+    """Against a row-by-row restatement: rows of a worker keep the batch plan's order, requests
+    are renumbered per worker, and a per-row flag array travels with its rows."""
+    from bikv_b200.coordinator import NativePrefixCacheCoordinator, PrefixReuseWorkload, split_by_worker
+    n_workers = 3
+    co = NativePrefixCacheCoordinator(2, 4096, 16)
+    wl = PrefixReuseWorkload(seed=3, n_users=50, n_workers=n_workers, n_requests=256, batch=64)
+    for batch in wl.batches():
+        bp = co.plan_batch(batch)
+        flags = (bp.gather.table[:, 0] % 3 == 0)
+        parts, part_flags = split_by_worker(bp, n_workers, gather_flags=flags)
+        local, seen = {}, [0] * n_workers
+        for i, r in enumerate(batch):
+            local[i] = seen[r.worker]
+            seen[r.worker] += 1
+        for k in range(n_workers):
+            assert [r.request_id for r in parts[k].requests] == [r.request_id for r in batch if r.worker == k]
+            for plan, part in ((bp.gather, parts[k].gather), (bp.scatter, parts[k].scatter)):
+                want = [[p, v, local[q], o] for p, v, q, o in plan.table.tolist() if batch[q].worker == k]
+                assert part.table.tolist() == want
+            want_flags = [bool(f) for f, row in zip(flags, bp.gather.table.tolist()) if batch[row[2]].worker == k]
+            assert part_flags[k].tolist() == want_flags
+        assert split_by_worker(bp, n_workers)[0].gather.table.tolist() == parts[0].gather.table.tolist()

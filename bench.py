@@ -57,9 +57,10 @@ def parse_args():
     ap.add_argument("--c3-order", default="longest", choices=["longest", "arrival"],
                     help="config3: stream each rank's requests longest first (balances the ranks' phases) or in arrival order")
     ap.add_argument("--c4-requests", type=int, default=20000)
-    ap.add_argument("--c4-placement", default="item", choices=["item", "striped"],
-                    help="config 4: 'item' = an item's pages live on ONE shard, chosen by the multi-shard page manager as "
-                         "in the reference; 'striped' = one page directory over all shards, page id mod shards")
+    ap.add_argument("--c4-placement", default="striped", choices=["item", "striped"],
+                    help="config 4: 'striped' = one page directory over all shards, page id mod shards (every shard serves "
+                         "a share of every item); 'item' = an item's pages live on ONE shard, chosen by the multi-shard "
+                         "page manager as in the reference (the shard holding the most popular users is the bottleneck)")
     ap.add_argument("--c4-planner", default="native", choices=["native", "python"],
                     help="config4: page directory in C++ (bikv_pm_*) or the Python page managers (order='fast')")
     ap.add_argument("--geometry", default="B", choices=["A", "B", "C", "R"],
@@ -521,9 +522,15 @@ def run_config4(ctx):
     Hazard: a prefix stored by batch k and read by batch k+1.  The planner sees it (page ids of
     the two plans intersect); those gather rows wait, on every shard, for a barrier behind the
     workers' scatters, the rest overlaps them.  Planning (all workers' shares, replicated on every
-    rank so that all hold the same page directory) runs on a host thread ahead of the kernels.  A
+    rank so that all hold the same page directory) runs on a host thread ahead of the kernels, and
+    every rank builds step k+1's rows and request tables while step k's kernels run.  A
     batch is planned in ONE piece and then split by worker: a user named twice in a batch, by
     requests of two workers, is stored by the first and not read by the second.
+
+    Placement (``--c4-placement``).  By default pages are striped over the shards (one page
+    directory, page id mod shards): with Zipf users, an item kept whole on one shard -- the
+    reference's ``MultiPageManager.load_item`` -- makes the shard with the most popular prefixes
+    push 45 % of all hit bytes on four shards, and a step lasts as long as that shard's push.
 
     Before the timed run a shorter stream goes through the same pipeline with closed-form
     contents: every prefix a miss stores is a function of (user, token, word), and every prefix

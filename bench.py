@@ -1128,6 +1128,7 @@ def workload_sides(args, ctx_base):
             out["config4_3200_requests"] = {k: c4[k] for k in keep if k in c4}
             if "config" in c4:
                 out["config4_3200_requests"]["workload"] = c4["config"]["workload"]
+                out["config4_3200_requests"]["placement"] = c4["config"].get("placement")
     return out
 
 

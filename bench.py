@@ -550,7 +550,7 @@ def run_config4(ctx):
     from bikv_b200 import selfcheck as S
     from bikv_b200 import workloads as W
     from bikv_b200.coordinator import (NativePrefixCacheCoordinator, PrefixCacheCoordinator, PrefixReuseWorkload,
-                                       split_by_worker)
+                                       plan_stream)
     from bikv_b200.plan import Plan
     from bikv_b200.push import split_plans_by_owner
 
@@ -620,17 +620,9 @@ def run_config4(ctx):
     def planner(wl, co, out_q):
         """Every worker's share of every batch, and which gather rows read a page the batch before
         writes (decided over ALL workers, so every rank decides alike)."""
-        being_written = np.zeros(n_shards * args.pool_pages, dtype=bool)     # by the batch before
-        prev_written = np.zeros(0, dtype=np.int32)
         try:
-            for batch in wl.batches():
-                bp = co.plan_batch(batch)
-                late = being_written[bp.gather.table[:, 0]]
-                being_written[prev_written] = False
-                prev_written = bp.scatter.table[:, 0].copy()
-                being_written[prev_written] = True
-                plans, late_masks = split_by_worker(bp, n_workers, gather_flags=late, transient=True)
-                out_q.put((plans, late_masks, bool(late.any())))
+            for step in plan_stream(wl.batches(), co, n_workers, n_shards * args.pool_pages, transient=True):
+                out_q.put(step)
         finally:
             out_q.put(None)
 

@@ -264,3 +264,23 @@ def split_by_worker(bp: BatchPlan, n_workers: int, gather_flags: Optional[np.nda
         idx = by_worker[first_req[k]:first_req[k + 1]]
         out.append(BatchPlan([bp.requests[i] for i in idx], gathers[k], scatters[k], [bp.hit[i] for i in idx]))
     return out if gather_flags is None else (out, flags)
+
+
+def plan_stream(batches, coordinator, n_workers: int, total_pages: int, transient: bool = False):
+    """For a pipeline that gathers batch k+1 while batch k is still being scattered: yields, per
+    batch, ``(plans, late, any_late)`` -- one plan per worker (:func:`split_by_worker` of the
+    batch planned in one piece), per worker a boolean array marking the gather rows that read a
+    page the batch BEFORE writes (a prefix stored by batch k and asked for again in batch k+1;
+    those rows must wait for that scatter), and whether any row is marked.  ``total_pages``:
+    page ids are below it.  Decided over all workers' rows, so every rank that replays the
+    same stream decides alike."""
+    being_written = np.zeros(int(total_pages), dtype=bool)       # by the batch before
+    prev_written = np.zeros(0, dtype=np.int32)
+    for batch in batches:
+        bp = coordinator.plan_batch(batch)
+        late = being_written[bp.gather.table[:, 0]]
+        being_written[prev_written] = False
+        prev_written = bp.scatter.table[:, 0].copy()
+        being_written[prev_written] = True
+        plans, masks = split_by_worker(bp, n_workers, gather_flags=late, transient=transient)
+        yield plans, masks, bool(late.any())

@@ -167,3 +167,24 @@ def test_split_by_worker_keeps_row_order_and_splits_row_flags(native):
             want_flags = [bool(f) for f, row in zip(flags, bp.gather.table.tolist()) if batch[row[2]].worker == k]
             assert part_flags[k].tolist() == want_flags
         assert split_by_worker(bp, n_workers)[0].gather.table.tolist() == parts[0].gather.table.tolist()
+
+
+def test_plan_stream_marks_gather_rows_that_read_what_the_batch_before_writes(native):
+    """The late flags of batch k+1 are exactly the gather rows whose page batch k scatters into,
+    for the striped (one directory) and the item-per-shard placement alike."""
+    from bikv_b200.coordinator import NativePrefixCacheCoordinator, PrefixReuseWorkload, plan_stream
+    for dirs, pages in ((1, 65536), (2, 32768)):
+        co = NativePrefixCacheCoordinator(dirs, pages, 16, transient_plans=True)
+        wl = PrefixReuseWorkload(seed=5, n_users=40, n_workers=2, n_requests=640, batch=64)
+        prev_pages, n_late, n_steps = set(), 0, 0
+        for plans, late, any_late in plan_stream(wl.batches(), co, 2, dirs * pages, transient=True):
+            want_any = False
+            for p, m in zip(plans, late):
+                want = [int(pg) in prev_pages for pg in p.gather.table[:, 0]]
+                assert m.tolist() == want
+                want_any |= any(want)
+            assert any_late == want_any
+            n_late += any_late
+            n_steps += 1
+            prev_pages = set(int(pg) for p in plans for pg in p.scatter.table[:, 0])
+        assert n_steps == 10 and n_late > 0          # 40 users: repeats across neighbouring batches are certain
